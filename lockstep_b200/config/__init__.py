@@ -2,12 +2,14 @@
 
 from .registry import (architecture_name, config_from_dict, known_architectures, load_config,
                        register_architecture, unregister_architecture)
-from .spec import ConfigError, LayerRun, LayerSpec, ModelSpec, PartSpec
+from .spec import ConfigError, LayerRun, LayerSpec, ModelSpec, PartSpec, own_tensors, tensor_name
 from . import qwen3 as _qwen3  # registers Qwen3ForCausalLM
 from .qwen3 import Qwen3Config
+from . import sevipel as _sevipel  # registers Sevipel
+from .sevipel import SevipelConfig
 
 __all__ = [
-    "ConfigError", "LayerRun", "LayerSpec", "ModelSpec", "PartSpec", "Qwen3Config",
+    "ConfigError", "LayerRun", "LayerSpec", "ModelSpec", "PartSpec", "Qwen3Config", "SevipelConfig",
     "architecture_name", "config_from_dict", "known_architectures", "load_config",
-    "register_architecture", "unregister_architecture",
+    "own_tensors", "register_architecture", "tensor_name", "unregister_architecture",
 ]

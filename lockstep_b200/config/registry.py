@@ -1,7 +1,7 @@
 """One registry from an architecture's name to its configuration class.
 
-``config.json`` names its architecture in ``architectures[0]`` (``model_type``
-is accepted where that list is absent).  The configuration class reads the
+``config.json`` names its architecture in ``architectures[0]`` (a plain string under
+``architecture``, or ``model_type``, is accepted where that list is absent).  The configuration class reads the
 architecture's own keys and builds the ``ModelSpec``; the generic model in
 ``engine.model`` is assembled from that spec, so registering an architecture
 means registering a configuration class and, if it needs them, new parts.
@@ -48,6 +48,9 @@ def architecture_name(raw: Mapping[str, Any]) -> str:
     archs = raw.get("architectures")
     if isinstance(archs, (list, tuple)) and archs:
         return str(archs[0])
+    single = raw.get("architecture")
+    if isinstance(single, str) and single:
+        return single
     mt = raw.get("model_type")
     if mt in _MODEL_TYPES:
         return _MODEL_TYPES[mt]

@@ -87,11 +87,15 @@ class ModelSpec:
     # tensor-name prefixes of the parts that are not layers
     names: Mapping[str, str] = field(default_factory=lambda: {
         "embedding": "model.embed_tokens", "final_norm": "model.norm", "head": "lm_head"})
+    # tensors a model folder may hold although this model reads none of them (say, the norm in
+    # front of a feed-forward that the layer does not have)
+    optional_tensors: tuple[str, ...] = ()
 
     def __post_init__(self):
         object.__setattr__(self, "names", _freeze(self.names))
         object.__setattr__(self, "layers", tuple(self.layers))
         object.__setattr__(self, "schedule", tuple(self.schedule))
+        object.__setattr__(self, "optional_tensors", tuple(self.optional_tensors))
         writers: dict[int, int] = {}
         for run in self.schedule:
             if not 0 <= run.layer < len(self.layers):
@@ -106,6 +110,20 @@ class ModelSpec:
     @property
     def cache_entries(self) -> int:
         return 1 + max((run.cache for run in self.schedule), default=-1)
+
+
+def tensor_name(prefix: str, local: str) -> str:
+    """The full name of a part's tensor: a part may name a tensor "" to own its prefix itself
+    (an embedding stored as ``embed`` rather than ``embed.weight``)."""
+    return f"{prefix}.{local}" if local else prefix
+
+
+def own_tensors(prefix: str, tensors: Mapping[str, Any]) -> dict[str, Any]:
+    """The entries of ``tensors`` that lie under ``prefix``, by their local names."""
+    out = {k[len(prefix) + 1:]: v for k, v in tensors.items() if k.startswith(prefix + ".")}
+    if prefix in tensors:
+        out[""] = tensors[prefix]
+    return out
 
 
 class ConfigError(ValueError):

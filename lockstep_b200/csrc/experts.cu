@@ -1,0 +1,263 @@
+// A feed-forward of routed experts: router scores, the choice of the top experts per token,
+// the step's (token, choice) pairs sorted by expert, the experts' two products over the
+// sorted rows, and the sum of a token's choices into the residual stream.
+//
+// Router logits arrive as float32 [tokens, experts].  The score is the sigmoid of the logit;
+// the `top` largest are chosen (ties to the lower index) and kept in order of rank.  A pair's
+// row in the sorted order is handed out by a counter per expert, so which row a pair gets
+// may differ from run to run, but no value depends on it: every element of a product is one
+// chain of fused multiply-adds over ascending k, whatever tile its row lies in, and a token's
+// choices are added in order of rank.
+#include "common.cuh"
+
+namespace {
+
+constexpr int MAX_PER_LANE = 16;      // experts a lane looks after: up to 512 experts
+constexpr int ROUTE_WARPS = 8;
+constexpr int PLAN_THREADS = 1024;
+constexpr int TILE_M = 64, TILE_N = 64, TILE_K = 16;
+
+// ids [T, top] int32, weights [T, top] float32
+__global__ void __launch_bounds__(ROUTE_WARPS * 32) route_kernel(const float* __restrict__ logits, int tokens, int experts,
+                                                                 int top, int* __restrict__ ids,
+                                                                 float* __restrict__ weights) {
+  ls_dependency_sync();
+  const int lane = threadIdx.x & 31, t = blockIdx.x * ROUTE_WARPS + (threadIdx.x >> 5);
+  if (t >= tokens) return;
+  float z[MAX_PER_LANE];
+#pragma unroll
+  for (int i = 0; i < MAX_PER_LANE; ++i) {
+    const int e = lane + 32 * i;
+    z[i] = e < experts ? logits[(int64_t)t * experts + e] : -INFINITY;
+  }
+  unsigned taken = 0;
+  for (int r = 0; r < top; ++r) {
+    float best = -INFINITY;
+    int at = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < MAX_PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      if (e < experts && !((taken >> i) & 1u) && (z[i] > best || (z[i] == best && e < at))) {
+        best = z[i];
+        at = e;
+      }
+    }
+    for (int off = 16; off > 0; off >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, off);
+      if (ob > best || (ob == best && oa < at)) {
+        best = ob;
+        at = oa;
+      }
+    }
+    if ((at & 31) == lane) taken |= 1u << (at >> 5);
+    if (lane == 0) {
+      ids[(int64_t)t * top + r] = at;
+      weights[(int64_t)t * top + r] = 1.0f / (1.0f + expf(-best));
+    }
+  }
+}
+
+// plan [0] = tiles, then (expert, first row, rows) per tile; row_token / row_weight per sorted
+// row; pair_row [T * top]: the sorted row of a pair
+__global__ void __launch_bounds__(PLAN_THREADS) plan_kernel(const int* __restrict__ ids, const float* __restrict__ weights,
+                                                            int pairs, int top, int experts, int* __restrict__ plan,
+                                                            int max_tiles, int* __restrict__ row_token,
+                                                            float* __restrict__ row_weight, int* __restrict__ pair_row,
+                                                            int* err) {
+  extern __shared__ int sm[];
+  int* count = sm;                  // [experts]
+  int* first = count + experts;     // [experts]
+  int* cursor = first + experts;    // [experts]
+  ls_dependency_sync();
+  const int tid = threadIdx.x;
+  for (int e = tid; e < experts; e += PLAN_THREADS) count[e] = cursor[e] = 0;
+  __syncthreads();
+  for (int p = tid; p < pairs; p += PLAN_THREADS) {
+    const int e = ids[p];
+    if (e >= 0 && e < experts) atomicAdd(&count[e], 1);
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int at = 0, tiles = 0;
+    for (int e = 0; e < experts; ++e) {
+      first[e] = at;
+      for (int r0 = 0; r0 < count[e]; r0 += TILE_M) {
+        if (tiles < max_tiles) {
+          plan[1 + 3 * tiles] = e;
+          plan[1 + 3 * tiles + 1] = at + r0;
+          plan[1 + 3 * tiles + 2] = count[e] - r0 < TILE_M ? count[e] - r0 : TILE_M;
+        }
+        ++tiles;
+      }
+      at += count[e];
+    }
+    if (tiles > max_tiles) {
+      ls_record_fault(err, LS_DEV_ROW_RANGE, tiles);
+      tiles = max_tiles;
+    }
+    plan[0] = tiles;
+  }
+  __syncthreads();
+  for (int p = tid; p < pairs; p += PLAN_THREADS) {
+    const int e = ids[p];
+    if (e < 0 || e >= experts) continue;
+    const int row = first[e] + atomicAdd(&cursor[e], 1);
+    row_token[row] = p / top;
+    row_weight[row] = weights[p];
+    pair_row[p] = row;
+  }
+}
+
+// One tile of an expert's product on the CUDA cores: C[rows, N] = A[rows, K] . W_e[N, K]^T.
+//   MODE 0 (up):   A row = x[row_token] * row_weight, C = relu(.)^2 in the engine's type
+//   MODE 1 (down): A row = act[row],                  C float32
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256) expert_product_kernel(const int* __restrict__ plan, const T* __restrict__ A,
+                                                             const int* __restrict__ row_token,
+                                                             const float* __restrict__ row_weight,
+                                                             const T* __restrict__ W, void* __restrict__ Cout, int N,
+                                                             int K) {
+  __shared__ float As[TILE_K][TILE_M + 4];
+  __shared__ float Bs[TILE_K][TILE_N + 4];
+  ls_dependency_sync();
+  const int tile = blockIdx.y;
+  if (tile >= plan[0]) return;
+  const int e = plan[1 + 3 * tile], row0 = plan[1 + 3 * tile + 1], rows = plan[1 + 3 * tile + 2];
+  const int n0 = blockIdx.x * TILE_N, tid = threadIdx.x;
+  const T* We = W + (int64_t)e * N * K;
+  const int ty = tid >> 4, tx = tid & 15;
+  float acc[4][4] = {};
+  // what this thread loads: four elements of A and of W per k-block
+  const int lr = tid >> 2, lk = (tid & 3) * 4;       // row (or weight row) 0..63, k 0, 4, 8, 12
+  int64_t a_row = -1;
+  float a_scale = 1.f;
+  if (lr < rows) {
+    a_row = MODE == 0 ? row_token[row0 + lr] : row0 + lr;
+    if (MODE == 0) a_scale = row_weight[row0 + lr];
+  }
+  const bool w_ok = n0 + lr < N;
+  for (int k0 = 0; k0 < K; k0 += TILE_K) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int k = k0 + lk + i;
+      float av = 0.f, wv = 0.f;
+      if (a_row >= 0 && k < K) {
+        av = ls_to_float<T>(A[a_row * K + k]);
+        if (MODE == 0) av = av * a_scale;
+      }
+      if (w_ok && k < K) wv = ls_to_float<T>(We[(int64_t)(n0 + lr) * K + k]);
+      As[lk + i][lr] = av;
+      Bs[lk + i][lr] = wv;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < TILE_K; ++kk) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        a[i] = As[kk][ty * 4 + i];
+        b[i] = Bs[kk][tx * 4 + i];
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = ty * 4 + i;
+    if (r >= rows) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n >= N) continue;
+      const int64_t at = (int64_t)(row0 + r) * N + n;
+      if (MODE == 0) {
+        const float v = fmaxf(acc[i][j], 0.f);
+        reinterpret_cast<T*>(Cout)[at] = ls_from_float<T>(v * v);
+      } else {
+        reinterpret_cast<float*>(Cout)[at] = acc[i][j];
+      }
+    }
+  }
+}
+
+// residual[t, :] += y[row of (t, 0), :] + y[row of (t, 1), :] + ... in order of rank
+__global__ void __launch_bounds__(256) combine_kernel(const float* __restrict__ y, const int* __restrict__ pair_row,
+                                                      float* __restrict__ residual, int top, int width) {
+  ls_dependency_sync();
+  const int t = blockIdx.x;
+  for (int c = threadIdx.x; c < width; c += 256) {
+    float sum = y[(int64_t)pair_row[(int64_t)t * top] * width + c];
+    for (int r = 1; r < top; ++r) sum += y[(int64_t)pair_row[(int64_t)t * top + r] * width + c];
+    residual[(int64_t)t * width + c] += sum;
+  }
+}
+
+}  // namespace
+
+LS_API int ls_experts_tile_rows() { return TILE_M; }
+
+LS_API int ls_experts_route(const float* logits, int tokens, int experts, int top, int* ids, float* weights,
+                            cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (experts <= 0 || experts > 32 * MAX_PER_LANE || top <= 0 || top > experts) return LS_E_SIZE;
+  LS_COUNT(LS_K_EXPERTS_ROUTE);
+  cudaError_t e = ls_launch(route_kernel, dim3((tokens + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), 0, stream,
+                            logits, tokens, experts, top, ids, weights);
+  if (e != cudaSuccess) return (int)e;
+  return ls_launch_status();
+}
+
+LS_API int ls_experts_plan(const int* ids, const float* weights, int tokens, int top, int experts, int* plan,
+                           int max_tiles, int* row_token, float* row_weight, int* pair_row, int* err,
+                           cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (experts <= 0 || experts > 4096 || top <= 0 || max_tiles <= 0) return LS_E_SIZE;
+  LS_COUNT(LS_K_EXPERTS_PLAN);
+  cudaError_t e = ls_launch(plan_kernel, dim3(1), dim3(PLAN_THREADS), sizeof(int) * 3 * (size_t)experts, stream, ids,
+                            weights, tokens * top, top, experts, plan, max_tiles, row_token, row_weight, pair_row, err);
+  if (e != cudaSuccess) return (int)e;
+  return ls_launch_status();
+}
+
+// mode 0: act[rows, N] = relu(x[row_token] * row_weight . W_e^T)^2; mode 1: y[rows, N] = act . W_e^T (float32).
+// W [experts, N, K] in the engine's type.
+LS_API int ls_experts_product(int mode, int dtype, const int* plan, int max_tiles, const void* A, const int* row_token,
+                              const float* row_weight, const void* W, void* C, int N, int K, cudaStream_t stream) {
+  if (max_tiles <= 0) return 0;
+  if (N <= 0 || K <= 0 || max_tiles > 65535) return LS_E_SIZE;
+  const dim3 grid((N + TILE_N - 1) / TILE_N, max_tiles);
+  LS_COUNT(mode == 0 ? LS_K_EXPERTS_UP : LS_K_EXPERTS_DOWN);
+  cudaError_t e;
+  typedef __nv_bfloat16 bf16;
+  if (dtype == LS_F32 && mode == 0)
+    e = ls_launch(expert_product_kernel<float, 0>, grid, dim3(256), 0, stream, plan, (const float*)A, row_token, row_weight, (const float*)W, C, N, K);
+  else if (dtype == LS_F32 && mode == 1)
+    e = ls_launch(expert_product_kernel<float, 1>, grid, dim3(256), 0, stream, plan, (const float*)A, row_token, row_weight, (const float*)W, C, N, K);
+  else if (dtype == LS_BF16 && mode == 0)
+    e = ls_launch(expert_product_kernel<bf16, 0>, grid, dim3(256), 0, stream, plan, (const bf16*)A, row_token, row_weight, (const bf16*)W, C, N, K);
+  else if (dtype == LS_BF16 && mode == 1)
+    e = ls_launch(expert_product_kernel<bf16, 1>, grid, dim3(256), 0, stream, plan, (const bf16*)A, row_token, row_weight, (const bf16*)W, C, N, K);
+  else return LS_E_DTYPE;
+  if (e != cudaSuccess) return (int)e;
+  return ls_launch_status();
+}
+
+LS_API int ls_experts_combine(const float* y, const int* pair_row, float* residual, int tokens, int top, int width,
+                              cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  LS_COUNT(LS_K_EXPERTS_COMBINE);
+  cudaError_t e = ls_launch(combine_kernel, dim3(tokens), dim3(256), 0, stream, y, pair_row, residual, top, width);
+  if (e != cudaSuccess) return (int)e;
+  return ls_launch_status();
+}
+
+LS_API const char* ls_constants_experts() {
+  static char buf[256];
+  static const LsConstant c[] = {{"experts.tile_rows", TILE_M}, {"experts.tile_features", TILE_N}, {"experts.k_block", TILE_K}};
+  return ls_format_constants(buf, sizeof buf, c, (int)(sizeof c / sizeof c[0]));
+}

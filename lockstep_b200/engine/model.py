@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import torch
 
-from ..config.spec import ModelSpec
+from ..config.spec import ModelSpec, own_tensors, tensor_name
 from ..parts import Runtime, WeightSpec, build_part
 
 
@@ -36,29 +36,37 @@ class Model:
         out: dict[str, WeightSpec] = {}
         for prefix, part in self._named_parts():
             for local, spec in part.weight_specs().items():
-                out[f"{prefix}.{local}"] = spec
+                out[tensor_name(prefix, local)] = spec
         return out
 
     def aliases(self) -> dict[str, str]:
         """Names the file may store although the model takes them from another tensor."""
         n = self.spec.names
-        return {f"{n['head']}.weight": f"{n['embedding']}.weight"} if self.tied_head else {}
+        if not self.tied_head:
+            return {}
+        table = tensor_name(n["embedding"], next(iter(self.embedding.weight_specs())))
+        return {f"{n['head']}.weight": table}
 
     def bind(self, tensors: dict[str, torch.Tensor]) -> None:
         for prefix, part in self._named_parts():
-            own = {k[len(prefix) + 1:]: v for k, v in tensors.items() if k.startswith(prefix + ".")}
+            own = own_tensors(prefix, tensors)
             if part is self.head and self.tied_head:
-                own = {"weight": tensors[f"{self.spec.names['embedding']}.weight"]}
+                own = {"weight": self.embedding.table}
             if own or part.weight_specs():
                 part.bind(own)
 
     # -- cache --------------------------------------------------------------
     def cache_needs(self):
-        """For each cache entry of the schedule, the need of the layer that writes it."""
+        """For each cache entry of the schedule, the need of the layer that writes it, widened
+        to what the layers that only read it ask for (a reader with a longer window, or none,
+        keeps the writer's pages alive that long)."""
         needs = [None] * self.spec.cache_entries
         for run in self.spec.schedule:
             if run.writes_cache:
                 needs[run.cache] = self.blocks[run.layer].cache_need()
+        for run in self.spec.schedule:
+            if not run.writes_cache and needs[run.cache] is not None:
+                needs[run.cache] = needs[run.cache].widened(self.blocks[run.layer].cache_need())
         return needs
 
 

@@ -33,7 +33,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--max-tokens", type=int, required=True,
                    help="most tokens live requests hold at any time (each rounded up to 64)")
     p.add_argument("--page-size", type=int, default=16, help="tokens per cache page (default 16)")
-    p.add_argument("--max-live", type=int, default=16, help="most requests live at a time")
+    p.add_argument("--max-live", type=int, default=4,
+                   help="most requests live at a time: rows of the block tables and state slots (default 4)")
     p.add_argument("--device", default="cuda:0")
     return p
 

@@ -57,7 +57,8 @@ class ModelRunner:
         self.model = Model(self.spec, self.rt)
         self._cast_report: dict = {}
         tensors = load_weights(Path(model_dir), self.model.weight_specs(), self.dtype, self.device,
-                               aliases=self.model.aliases(), report=self._cast_report)
+                               aliases=self.model.aliases(), report=self._cast_report,
+                               optional=self.spec.optional_tensors)
         self.model.bind(tensors)
         self.cache = CacheManager(self.model.cache_needs(), num_pages=num_pages, page_size=page_size,
                                   max_live=max_live, max_seq_len=self.max_seq_len, dtype=self.dtype,

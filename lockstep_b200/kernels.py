@@ -87,6 +87,31 @@ _SIGNATURES["tc"] = {
                       c_int, c_void_p, c_void_p],
 }
 
+_SIGNATURES["seq"] = {
+    "ls_qkv_finish": [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                      c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                      c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p],
+    "ls_find_portions": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p],
+    "ls_delta_prep": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                      c_int, c_int, c_float, c_void_p],
+    "ls_shift_mix": [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int, c_int, c_int,
+                     c_void_p],
+    "ls_lowrank_decay": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "ls_state_rule": [c_int, c_int, c_void_p, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
+                      c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int,
+                      c_void_p],
+    "ls_head_rms_gate": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                         c_float, c_void_p],
+    "ls_experts_tile_rows": [],
+    "ls_experts_route": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+    "ls_experts_plan": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                        c_void_p, c_void_p],
+    "ls_experts_product": [c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                           c_int, c_void_p],
+    "ls_experts_combine": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+}
+
 _libs: dict[str, ctypes.CDLL] = {}
 
 
@@ -124,7 +149,7 @@ def set_attention_prefill_pairs(mode: int) -> None:
 def set_dependent_launch(on: bool) -> None:
     """Programmatic dependent launch of all kernels (on by default): a kernel is
     scheduled while its predecessor drains and waits for it before it touches memory."""
-    for name in ("core", "tc"):
+    for name in ["core", "tc"] + [n for n in _libs if n not in ("core", "tc")]:
         fn = getattr(library(name), f"ls_set_dependent_launch_{name}")
         fn.argtypes, fn.restype = [c_int], None
         fn(1 if on else 0)
@@ -420,7 +445,7 @@ def gemm_nt_tc(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int,
     status = library("tc").ls_gemm_nt_tc(
         _dev(a, "a"), _dev(w, "w"), _dev(c, "c"), _code(c), m, n, k, k, k, n, epilogue,
         _dev(err, "err", torch.int32), _stream())
-    if status == -3:
+    if status in (-2, -3):
         return False
     _check(status, "gemm_nt_tc")
     return True
@@ -521,3 +546,152 @@ def gemm_nt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = E
         if gemm_nt_tc(a, w, c, epilogue, err):
             return
     gemm_nt_simt(a, w, c, epilogue)
+
+
+# ---------------------------------------------------------------------------
+# library "seq": heads of unequal sizes, mixers with a carried state, routed experts
+# ---------------------------------------------------------------------------
+
+RULE_DELTA, RULE_WKV = 0, 1
+
+
+def qkv_finish(qkv, q_out, pages, q_gain, k_gain, cos, sin, positions, token_req, block_table, nq: int, nkv: int,
+               d: int, dv: int, pad: int, rot_dim: int, eps: float, whole_projection: bool, has_kv: bool,
+               write_cache: bool, err) -> None:
+    """Finishes a projection ``qkv`` [tokens, nq*d (+ nkv*d + nkv*dv)]: RMSNorm of q and of k (over
+    the whole projection, or per head), rotation of the first ``rot_dim`` elements of each head,
+    queries to ``q_out`` [tokens, nq*pad] and keys and values into ``pages``
+    [num_pages, 2, nkv, page_size, pad], padded with zeros (csrc/heads_wide.cu)."""
+    tokens = qkv.shape[0]
+    cols = nq * d + (nkv * (d + dv) if has_kv else 0)
+    if qkv.shape[1] != cols or q_out.shape != (tokens, nq * pad) or q_out.dtype != qkv.dtype:
+        raise KernelError("qkv_finish: shapes do not agree")
+    gains = [g for g in (q_gain, k_gain) if g is not None]
+    if any(g.dtype != gains[0].dtype for g in gains):
+        raise KernelError("qkv_finish: gains of two element types")
+    want_q = nq * d if whole_projection else d
+    want_k = nkv * d if whole_projection else d
+    if (q_gain is not None and q_gain.numel() != want_q) or (k_gain is not None and k_gain.numel() != want_k):
+        raise KernelError("qkv_finish: gains do not match the projection")
+    if write_cache:
+        if pages.dtype != qkv.dtype or pages.shape[1:3] != (2, nkv) or pages.shape[4] != pad:
+            raise KernelError("qkv_finish: cache pages do not match the projections")
+        num_pages, page_size = pages.shape[0], pages.shape[3]
+    else:
+        num_pages, page_size = 0, 1
+    if rot_dim and (cos.shape != sin.shape or cos.shape[1] != rot_dim // 2):
+        raise KernelError("qkv_finish: rotary tables do not match rot_dim")
+    _check(library("seq").ls_qkv_finish(
+        _dev(qkv, "qkv"), qkv.shape[1], _dev(q_out, "q_out"), _opt(pages if write_cache else None, "pages"),
+        _code(qkv), _opt(q_gain, "q_gain"), _opt(k_gain, "k_gain"), _code(gains[0]) if gains else F32,
+        _opt(cos if rot_dim else None, "cos", torch.float32), _opt(sin if rot_dim else None, "sin", torch.float32),
+        _dev(positions, "positions", torch.int32), _dev(token_req, "token_req", torch.int32),
+        _dev(block_table, "block_table", torch.int32), block_table.shape[-1], tokens, nq, nkv, d, dv, pad, rot_dim,
+        page_size, num_pages, cos.shape[0] if rot_dim else 0, float(eps), 2 if whole_projection else 1,
+        1 if has_kv else 0, 1 if write_cache else 0, _dev(err, "err", torch.int32), _stream()), "qkv_finish")
+
+
+def find_portions(token_slot, out, cap: int, err) -> None:
+    """out int32 [1 + 3 cap]: the number of portions of the step's token axis, then (first token,
+    tokens, slot) of each, from ``token_slot`` alone (csrc/recurrent.cu)."""
+    if out.numel() < 1 + 3 * cap:
+        raise KernelError("find_portions: the list is too short")
+    _check(library("seq").ls_find_portions(_dev(token_slot, "token_slot", torch.int32), token_slot.numel(),
+                                           _dev(out, "out", torch.int32), cap, _dev(err, "err", torch.int32),
+                                           _stream()), "find_portions")
+
+
+def delta_prep(proj, conv_w, w_a2, dt_bias, a_log, w_g2, state, token_slot, qkv, decay, beta, gate, heads: int,
+               groups: int, dk: int, dv: int, taps: int, unit_eps: float) -> None:
+    """What lies between the projections and the gated delta rule, a token a block: causal
+    convolution (carried inputs from ``state``) and silu of q, k, v, unit q and k, beta, the decay
+    per key channel and the output gate through their low-rank maps; float32 out."""
+    f32 = torch.float32
+    _check(library("seq").ls_delta_prep(
+        _dev(proj, "proj"), proj.shape[1], _code(proj), _dev(conv_w, "conv_w", f32), _dev(w_a2, "w_a2", proj.dtype),
+        _dev(dt_bias, "dt_bias", f32), _dev(a_log, "a_log", f32), _dev(w_g2, "w_g2", proj.dtype),
+        _dev(state, "state", f32), state.shape[1], _dev(token_slot, "token_slot", torch.int32), _dev(qkv, "qkv", f32),
+        _dev(decay, "decay", f32), _dev(beta, "beta", f32), _dev(gate, "gate", f32), proj.shape[0], heads, groups,
+        dk, dv, taps, w_a2.shape[1], w_g2.shape[1], float(unit_eps), _stream()), "delta_prep")
+
+
+def shift_mix(x, mu, state, prev_offset: int, token_slot, out) -> None:
+    """out[s, t] = x[t] + (x[t - 1] - x[t]) * mu[s], the token before a portion's first one taken
+    from ``state[slot, prev_offset:]``."""
+    tokens, width = x.shape
+    if out.shape != (mu.shape[0], tokens, width) or out.dtype != x.dtype:
+        raise KernelError("shift_mix: shapes do not agree")
+    _check(library("seq").ls_shift_mix(
+        _dev(x, "x"), _code(x), _dev(mu, "mu", torch.float32), _dev(state, "state", torch.float32), state.shape[1],
+        prev_offset, _dev(token_slot, "token_slot", torch.int32), _dev(out, "out"), tokens, width, mu.shape[0],
+        _stream()), "shift_mix")
+
+
+def lowrank_decay(low, w2, w0, decay) -> None:
+    """decay[t, i] = exp(-exp(w2[i] . tanh(low[t]) + w0[i])), float32."""
+    tokens, rank = low.shape
+    if w2.shape[1] != rank or decay.shape != (tokens, w2.shape[0]) or w2.dtype != low.dtype:
+        raise KernelError("lowrank_decay: shapes do not agree")
+    _check(library("seq").ls_lowrank_decay(_dev(low, "low"), _dev(w2, "w2"), _code(low), _dev(w0, "w0", torch.float32),
+                                           _dev(decay, "decay", torch.float32), tokens, w2.shape[0], rank, _stream()),
+           "lowrank_decay")
+
+
+def state_rule(rule: int, dtype, portions, max_portions: int, state, in_a, in_b, in_v, decay, beta, bonus, out,
+               carry_src, carry_width: int, carry_rows: int, heads: int, groups: int, dk: int, dv: int) -> None:
+    """Walks every portion of the step through a state rule (RULE_DELTA, RULE_WKV), reading and
+    writing ``state[slot]`` (float32: the matrix state, then the carried inputs)."""
+    _check(library("seq").ls_state_rule(
+        rule, _DTYPE_CODE[dtype], _dev(portions, "portions", torch.int32), max_portions,
+        _dev(state, "state", torch.float32), state.shape[1], _dev(in_a, "in_a"), _opt(in_b, "in_b"), _opt(in_v, "in_v"),
+        _dev(decay, "decay", torch.float32), _opt(beta, "beta", torch.float32), _opt(bonus, "bonus", torch.float32),
+        _dev(out, "out", torch.float32), _dev(carry_src, "carry_src", dtype), carry_src.shape[1], carry_width,
+        carry_rows, heads, groups, dk, dv, _stream()), "state_rule")
+
+
+def head_rms_gate(o, gain, gate_f32, gate_x, out, heads: int, dv: int, gain_shared: bool, eps: float) -> None:
+    """out = o / rms_per_head(o) * gain * gate, where the gate is ``gate_f32`` as it is or
+    silu(``gate_x``)."""
+    _check(library("seq").ls_head_rms_gate(
+        _dev(o, "o", torch.float32), _dev(gain, "gain", torch.float32), _opt(gate_f32, "gate_f32", torch.float32),
+        _opt(gate_x, "gate_x", out.dtype), _dev(out, "out"), _code(out), o.shape[0], heads, dv,
+        1 if gain_shared else 0, float(eps), _stream()), "head_rms_gate")
+
+
+def experts_tile_rows() -> int:
+    return int(library("seq").ls_experts_tile_rows())
+
+
+def experts_route(logits, top: int, ids, weights) -> None:
+    tokens, experts = logits.shape
+    _check(library("seq").ls_experts_route(_dev(logits, "logits", torch.float32), tokens, experts, top,
+                                           _dev(ids, "ids", torch.int32), _dev(weights, "weights", torch.float32),
+                                           _stream()), "experts_route")
+
+
+def experts_plan(ids, weights, experts: int, plan, max_tiles: int, row_token, row_weight, pair_row, err) -> None:
+    tokens, top = ids.shape
+    _check(library("seq").ls_experts_plan(
+        _dev(ids, "ids", torch.int32), _dev(weights, "weights", torch.float32), tokens, top, experts,
+        _dev(plan, "plan", torch.int32), max_tiles, _dev(row_token, "row_token", torch.int32),
+        _dev(row_weight, "row_weight", torch.float32), _dev(pair_row, "pair_row", torch.int32),
+        _dev(err, "err", torch.int32), _stream()), "experts_plan")
+
+
+def experts_product(mode: int, plan, max_tiles: int, a, row_token, row_weight, w, c) -> None:
+    """mode 0: c[row] = relu((a[row_token[row]] * row_weight[row]) @ w[e].T)^2; mode 1: c[row] = a[row] @ w[e].T
+    in float32; rows sorted by expert as ``plan`` says.  w [experts, n, k]."""
+    n, k = w.shape[1], w.shape[2]
+    if a.shape[1] != k or c.shape[1] != n or a.dtype != w.dtype:
+        raise KernelError("experts_product: shapes do not agree")
+    _check(library("seq").ls_experts_product(
+        mode, _code(a), _dev(plan, "plan", torch.int32), max_tiles, _dev(a, "a"),
+        _dev(row_token, "row_token", torch.int32), _dev(row_weight, "row_weight", torch.float32), _dev(w, "w"),
+        _dev(c, "c"), n, k, _stream()), "experts_product")
+
+
+def experts_combine(y, pair_row, residual, top: int) -> None:
+    tokens, width = residual.shape
+    _check(library("seq").ls_experts_combine(_dev(y, "y", torch.float32), _dev(pair_row, "pair_row", torch.int32),
+                                             _dev(residual, "residual", torch.float32), tokens, top, width, _stream()),
+           "experts_combine")

@@ -23,10 +23,16 @@ from ..config.spec import PartSpec
 @dataclass(frozen=True)
 class WeightSpec:
     """A tensor a part needs.  role: "matrix" (used in a product), "table"
-    (looked up by integer id) or "gain" (a norm's scale vector)."""
+    (looked up by integer id) or "gain" (a norm's scale vector, or another small vector
+    that is used in float32).  An extent of -1 stands for whatever the stored tensor has
+    (the rank of a low-rank map that the configuration does not give)."""
 
     shape: tuple[int, ...]
     role: str = "matrix"
+
+    def fits(self, shape) -> bool:
+        shape = tuple(shape)
+        return len(shape) == len(self.shape) and all(w == -1 or w == s for w, s in zip(self.shape, shape))
 
 
 @dataclass(frozen=True)
@@ -45,6 +51,17 @@ class CacheNeed:
     window: int = 0
     state_shape: tuple[int, ...] = ()
     state_dtype: torch.dtype = torch.float32
+
+    def widened(self, reader: "CacheNeed | None") -> "CacheNeed":
+        """This need, kept for as long as ``reader`` (a layer that reads the entry without
+        writing it) also asks: the longer of the two windows, 0 standing for every key."""
+        if reader is None or self.kind != "paged_kv":
+            return self
+        if (reader.kind, reader.kv_heads, reader.head_dim) != (self.kind, self.kv_heads, self.head_dim):
+            raise ValueError("a layer reads a cache entry whose keys and values do not have its sizes")
+        window = 0 if (self.window == 0 or reader.window == 0) else max(self.window, reader.window)
+        return self if window == self.window else CacheNeed(
+            self.kind, kv_heads=self.kv_heads, head_dim=self.head_dim, window=window)
 
     def group_key(self):
         if self.kind == "paged_kv":

@@ -1,10 +1,12 @@
 """Arrangement of a layer's parts.  "pre_norm":
 h += mixer(norm_a(h)); h += feed_forward(norm_b(h))  (LockStep: engine/model/qwen3.py:242-287).
 The names under which the layer's tensors are stored are parameters of the
-arrangement, so the same arrangement serves architectures that name them otherwise."""
+arrangement, so the same arrangement serves architectures that name them otherwise.
+A layer whose feed-forward is of kind "none" is its mixer alone."""
 
 from __future__ import annotations
 
+from ..config.spec import own_tensors, tensor_name
 from .base import Block, Runtime, build_part, register_part
 
 _DEFAULT_NAMES = {
@@ -23,11 +25,13 @@ class PreNormBlock(Block):
         self.position = build_part("position", layer_spec.position, runtime)
         self.mixer_norm = build_part("norm", layer_spec.mixer_norm, runtime)
         self.mixer = build_part("mixer", layer_spec.mixer, runtime, position=self.position)
-        self.feed_forward_norm = build_part("norm", layer_spec.feed_forward_norm, runtime)
-        self.feed_forward = build_part("feed_forward", layer_spec.feed_forward, runtime)
+        self.feed_forward_norm = self.feed_forward = None
+        if layer_spec.feed_forward.kind != "none":
+            self.feed_forward_norm = build_part("norm", layer_spec.feed_forward_norm, runtime)
+            self.feed_forward = build_part("feed_forward", layer_spec.feed_forward, runtime)
 
     def _children(self):
-        return [(self.names[k], getattr(self, k)) for k in _DEFAULT_NAMES]
+        return [(self.names[k], getattr(self, k)) for k in _DEFAULT_NAMES if getattr(self, k) is not None]
 
     def cache_need(self):
         return self.mixer.cache_need()
@@ -43,12 +47,12 @@ class PreNormBlock(Block):
         out = {}
         for name, part in self._children():
             for local, spec in part.weight_specs().items():
-                out[f"{name}.{local}"] = spec
+                out[tensor_name(name, local)] = spec
         return out
 
     def bind(self, tensors):
         for name, part in self._children():
-            own = {k[len(name) + 1:]: v for k, v in tensors.items() if k.startswith(name + ".")}
+            own = own_tensors(name, tensors)
             if own or part.weight_specs():
                 part.bind(own)
 
@@ -66,12 +70,15 @@ class PreNormBlock(Block):
         self.feed_forward.forward(self._normed(self.feed_forward_norm, self.feed_forward, h), ctx, h)
 
     def steps(self):
-        return [(bool(self.mixer_norm.graph_safe and self.mixer.graph_safe and self.position.graph_safe), self._mix),
-                (bool(self.feed_forward_norm.graph_safe and self.feed_forward.graph_safe), self._feed_forward)]
+        out = [(bool(self.mixer_norm.graph_safe and self.mixer.graph_safe and self.position.graph_safe), self._mix)]
+        if self.feed_forward is not None:
+            out.append((bool(self.feed_forward_norm.graph_safe and self.feed_forward.graph_safe), self._feed_forward))
+        return out
 
     def forward(self, h, ctx, cache):
         self._mix(h, ctx, cache)
-        self._feed_forward(h, ctx, cache)
+        if self.feed_forward is not None:
+            self._feed_forward(h, ctx, cache)
 
 
 @register_part("block", "pre_norm")

@@ -13,15 +13,16 @@ from .base import Part, Runtime, WeightSpec, register_part
 class TokenEmbedding(Part):
     graph_safe = True
 
-    def __init__(self, vocab_size: int, width: int, runtime: Runtime):
+    def __init__(self, vocab_size: int, width: int, runtime: Runtime, tensor: str = "weight"):
         self.vocab, self.width, self.rt = int(vocab_size), int(width), runtime
+        self.tensor = str(tensor)     # local name of the table ("" where the part's prefix names it)
         self.table = None
 
     def weight_specs(self):
-        return {"weight": WeightSpec((self.vocab, self.width), "table")}
+        return {self.tensor: WeightSpec((self.vocab, self.width), "table")}
 
     def bind(self, tensors):
-        self.table = tensors["weight"]
+        self.table = tensors[self.tensor]
 
     def forward(self, ctx) -> torch.Tensor:
         """The float32 residual stream [tokens, width] of the step's tokens.  An
@@ -53,7 +54,7 @@ class LinearHead(Part):
 
 @register_part("embedding", "token_embedding")
 def _build_embedding(spec, runtime, **_):
-    return TokenEmbedding(spec["vocab_size"], spec["width"], runtime)
+    return TokenEmbedding(spec["vocab_size"], spec["width"], runtime, spec.get("tensor", "weight"))
 
 
 @register_part("head", "linear_head")

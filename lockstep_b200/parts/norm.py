@@ -1,5 +1,8 @@
 """RMSNorm: y = x * rsqrt(mean(x^2) + eps) * gain, all in float32
-(LockStep: engine/kernels/rmsnorm.py:30-38)."""
+(LockStep: engine/kernels/rmsnorm.py:30-38).  ``offset``: the stored tensor is the gain minus
+this number (a gain kept around zero: offset 1); the sum is made once, in float32, when the
+weights arrive.  ``tensor``: the local name of the stored tensor ("weight"; "" where the norm's
+own prefix names it)."""
 
 from __future__ import annotations
 
@@ -39,15 +42,18 @@ class NormedRows:
 class RMSNorm(Norm):
     graph_safe = True
 
-    def __init__(self, width: int, eps: float, runtime: Runtime):
+    def __init__(self, width: int, eps: float, runtime: Runtime, offset: float = 0.0, tensor: str = "weight"):
         self.width, self.eps, self.rt = int(width), float(eps), runtime
+        self.offset, self.tensor = float(offset), str(tensor)
         self.gain: torch.Tensor | None = None
 
     def weight_specs(self):
-        return {"weight": WeightSpec((self.width,), "gain")}
+        return {self.tensor: WeightSpec((self.width,), "gain")}
 
     def bind(self, tensors):
-        self.gain = tensors["weight"]
+        self.gain = tensors[self.tensor]
+        if self.offset:
+            self.gain = (self.gain.to(torch.float32) + self.offset).contiguous()
 
     def lazy(self, h, row_index=None) -> NormedRows:
         """The rows of ``h`` to be normalised, for a part that sets ``accepts_normed_rows``."""
@@ -62,4 +68,4 @@ class RMSNorm(Norm):
 
 @register_part("norm", "rmsnorm")
 def _build(spec, runtime, **_):
-    return RMSNorm(spec["width"], spec["eps"], runtime)
+    return RMSNorm(spec["width"], spec["eps"], runtime, spec.get("offset", 0.0), spec.get("tensor", "weight"))

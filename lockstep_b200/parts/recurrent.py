@@ -1,0 +1,179 @@
+"""Mixers that carry a fixed-size state per request instead of keys and values.
+
+Both keep, per head, a float32 matrix S [key channels, value channels] in the request's state
+slot, walk a portion token by token, and finish with a per-head RMSNorm and a gate before the
+output projection.  The slot also carries what the next portion needs of the tokens before it.
+
+"gated_delta" (per head, with a decay g per key channel):
+    S <- diag(g_t) S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t
+  q, k, v come through short causal convolutions (their last taps - 1 inputs are carried) and
+  silu; q and k are unit vectors per head, q scaled by dk^(-1/2); beta = sigmoid(W_b x);
+  g = exp(-exp(A_log) softplus(W_a2 W_a1 x + dt_bias)); the read-out is normed per head, times a
+  gain shared by the heads, times sigmoid(W_g2 W_g1 x).
+
+"wkv" (per head, with a decay w per key channel and a bonus u for the current token):
+    o_t = (S + diag(u) k_t v_t^T)^T r_t;  S <- diag(w_t) S + k_t v_t^T
+  r, k, v, the gate and the decay's low-rank map each read their own mix of the token and the
+  one before it (carried across portions): x + (x_prev - x) mu;  w = exp(-exp(W_w2 tanh(W_w1 m) +
+  w0)); the read-out is normed per head, times a gain over all heads, times silu(W_g m).
+
+The projections run as the engine's products (tensor cores in bfloat16); everything between
+them and the recurrence, the recurrence and the state are float32 (csrc/recurrent.cu).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import kernels as K
+from .base import CacheNeed, Mixer, Runtime, WeightSpec, register_part
+
+
+def portion_list(ctx, state: torch.Tensor, rt: Runtime):
+    """(device list, its capacity) of the step's portions, made once per step on the device
+    from ``ctx.token_slot`` and kept on the context for the other layers (a recorded step makes
+    it in its graph).  There are at most as many portions as state slots."""
+    made = getattr(ctx, "_portion_list", None)
+    if made is None:
+        cap = min(int(ctx.token_slot.numel()), int(state.shape[0]))
+        out = torch.empty(1 + 3 * cap, dtype=torch.int32, device=rt.device)
+        K.find_portions(ctx.token_slot, out, cap, rt.err)
+        made = ctx._portion_list = (out, cap)
+    return made
+
+
+def _f32(t: torch.Tensor) -> torch.Tensor:
+    return t.to(torch.float32).contiguous()
+
+
+class GatedDelta(Mixer):
+    graph_safe = True
+
+    def __init__(self, hidden_size, num_heads, num_kv_heads, key_dim, value_dim, conv_taps, norm_eps, unit_eps,
+                 runtime: Runtime, decay_rank=None, gate_rank=None):
+        if num_heads % num_kv_heads:
+            raise ValueError("num_heads must be a multiple of num_kv_heads")
+        if not 1 <= conv_taps <= 8:
+            raise ValueError(f"a convolution of {conv_taps} taps is not supported (1 to 8)")
+        if key_dim > 256:
+            raise ValueError(f"key_dim {key_dim} is not supported (up to 256)")
+        self.w, self.H, self.G = int(hidden_size), int(num_heads), int(num_kv_heads)
+        self.dk, self.dv, self.taps = int(key_dim), int(value_dim), int(conv_taps)
+        self.eps, self.unit_eps, self.rt = float(norm_eps), float(unit_eps), runtime
+        self.Kd, self.Vd = self.G * self.dk, self.H * self.dv
+        self.C = 2 * self.Kd + self.Vd
+        # ranks of the two low-rank maps; -1: whatever the stored tensors have
+        self.rank_a, self.rank_g = int(decay_rank or -1), int(gate_rank or -1)
+
+    def cache_need(self):
+        return CacheNeed("state", state_shape=(self.H * self.dk * self.dv + (self.taps - 1) * self.C,),
+                         state_dtype=torch.float32)
+
+    def weight_specs(self):
+        return {
+            "q": WeightSpec((self.Kd, self.w)), "k": WeightSpec((self.Kd, self.w)), "v": WeightSpec((self.Vd, self.w)),
+            "q.conv": WeightSpec((self.Kd, self.taps), "gain"), "k.conv": WeightSpec((self.Kd, self.taps), "gain"),
+            "v.conv": WeightSpec((self.Vd, self.taps), "gain"),
+            "b": WeightSpec((self.H, self.w)), "A_log": WeightSpec((self.H,), "gain"),
+            "norm": WeightSpec((self.dv,), "gain"),
+            "a1": WeightSpec((self.rank_a, self.w)), "a2": WeightSpec((self.H * self.dk, self.rank_a)),
+            "dt_bias": WeightSpec((self.H * self.dk,), "gain"),
+            "g1": WeightSpec((self.rank_g, self.w)), "g2": WeightSpec((self.Vd, self.rank_g)),
+            "o": WeightSpec((self.w, self.Vd)),
+        }
+
+    def bind(self, t):
+        if t["a1"].shape[0] != t["a2"].shape[1] or t["g1"].shape[0] != t["g2"].shape[1]:
+            raise ValueError("the two halves of a low-rank map do not have the same rank")
+        # one product for everything that reads the mixer's input
+        self.w_in = torch.cat([t["q"], t["k"], t["v"], t["b"], t["a1"], t["g1"]], dim=0).contiguous()
+        self.conv_w = _f32(torch.cat([t["q.conv"], t["k.conv"], t["v.conv"]], dim=0))
+        self.w_a2, self.w_g2, self.w_o = t["a2"].contiguous(), t["g2"].contiguous(), t["o"]
+        self.dt_bias, self.a_log, self.gain = _f32(t["dt_bias"]), _f32(t["A_log"]), _f32(t["norm"])
+
+    def forward(self, x, ctx, cache, residual):
+        rt, tokens = self.rt, residual.shape[0]
+        f32 = torch.float32
+        proj = rt.rows(tokens, self.w_in.shape[0])
+        K.gemm_nt(x, self.w_in, proj, err=rt.err)
+        qkv = rt.rows(tokens, self.C, dtype=f32)
+        decay = rt.rows(tokens, self.H * self.dk, dtype=f32)
+        beta = rt.rows(tokens, self.H, dtype=f32)
+        gate = rt.rows(tokens, self.Vd, dtype=f32)
+        K.delta_prep(proj, self.conv_w, self.w_a2, self.dt_bias, self.a_log, self.w_g2, cache.state, ctx.token_slot,
+                     qkv, decay, beta, gate, self.H, self.G, self.dk, self.dv, self.taps, self.unit_eps)
+        portions, cap = portion_list(ctx, cache.state, rt)
+        o = rt.rows(tokens, self.Vd, dtype=f32)
+        K.state_rule(K.RULE_DELTA, rt.dtype, portions, cap, cache.state, qkv, None, None, decay, beta, None, o,
+                     proj, self.C, self.taps - 1, self.H, self.G, self.dk, self.dv)
+        y = rt.rows(tokens, self.Vd)
+        K.head_rms_gate(o, self.gain, gate, None, y, self.H, self.dv, True, self.eps)
+        K.gemm_nt(y, self.w_o, residual, K.EPILOGUE_RESIDUAL, err=rt.err)
+
+
+class Wkv(Mixer):
+    graph_safe = True
+    MIXES = ("r", "k", "v", "g", "w")
+
+    def __init__(self, hidden_size, num_heads, head_dim, norm_eps, runtime: Runtime, decay_rank=None):
+        if head_dim > 256:
+            raise ValueError(f"head_dim {head_dim} is not supported (up to 256)")
+        self.w, self.H, self.d = int(hidden_size), int(num_heads), int(head_dim)
+        self.eps, self.rt = float(norm_eps), runtime
+        self.A = self.H * self.d
+        self.rank = int(decay_rank or -1)      # -1: whatever the stored tensors have
+
+    def cache_need(self):
+        return CacheNeed("state", state_shape=(self.H * self.d * self.d + self.w,), state_dtype=torch.float32)
+
+    def weight_specs(self):
+        specs = {f"mu.{s}": WeightSpec((self.w,), "gain") for s in self.MIXES}
+        specs.update({
+            "r": WeightSpec((self.A, self.w)), "k": WeightSpec((self.A, self.w)), "v": WeightSpec((self.A, self.w)),
+            "g": WeightSpec((self.A, self.w)), "w1": WeightSpec((self.rank, self.w)),
+            "w2": WeightSpec((self.A, self.rank)),
+            "w0": WeightSpec((self.A,), "gain"), "u": WeightSpec((self.H, self.d), "gain"),
+            "norm": WeightSpec((self.A,), "gain"), "o": WeightSpec((self.w, self.A)),
+        })
+        return specs
+
+    def bind(self, t):
+        if t["w1"].shape[0] != t["w2"].shape[1]:
+            raise ValueError("the two halves of the decay's low-rank map do not have the same rank")
+        self.mu = _f32(torch.stack([t[f"mu.{s}"] for s in self.MIXES]))
+        self.w_r, self.w_k, self.w_v, self.w_g = t["r"], t["k"], t["v"], t["g"]
+        self.w_w1, self.w_w2, self.w_o = t["w1"], t["w2"].contiguous(), t["o"]
+        self.w0, self.bonus, self.gain = _f32(t["w0"]), _f32(t["u"].reshape(-1)), _f32(t["norm"])
+
+    def forward(self, x, ctx, cache, residual):
+        rt, tokens = self.rt, residual.shape[0]
+        f32 = torch.float32
+        prev_offset = self.H * self.d * self.d
+        mixed = rt.rows(len(self.MIXES) * tokens, self.w).view(len(self.MIXES), tokens, self.w)
+        K.shift_mix(x, self.mu, cache.state, prev_offset, ctx.token_slot, mixed)
+        r, k, v, g = (rt.rows(tokens, self.A) for _ in range(4))
+        low = rt.rows(tokens, self.w_w1.shape[0])
+        for i, (w, out) in enumerate(((self.w_r, r), (self.w_k, k), (self.w_v, v), (self.w_g, g), (self.w_w1, low))):
+            K.gemm_nt(mixed[i], w, out, err=rt.err)
+        decay = rt.rows(tokens, self.A, dtype=f32)
+        K.lowrank_decay(low, self.w_w2, self.w0, decay)
+        portions, cap = portion_list(ctx, cache.state, rt)
+        o = rt.rows(tokens, self.A, dtype=f32)
+        K.state_rule(K.RULE_WKV, rt.dtype, portions, cap, cache.state, r, k, v, decay, None, self.bonus, o,
+                     x, self.w, 1, self.H, self.H, self.d, self.d)
+        y = rt.rows(tokens, self.A)
+        K.head_rms_gate(o, self.gain, None, g, y, self.H, self.d, False, self.eps)
+        K.gemm_nt(y, self.w_o, residual, K.EPILOGUE_RESIDUAL, err=rt.err)
+
+
+@register_part("mixer", "gated_delta")
+def _build_delta(spec, runtime, **_):
+    return GatedDelta(spec["hidden_size"], spec["num_heads"], spec["num_kv_heads"], spec["key_dim"],
+                      spec["value_dim"], spec["conv_taps"], spec["norm_eps"], spec.get("unit_eps", 1e-6), runtime,
+                      decay_rank=spec.get("decay_rank"), gate_rank=spec.get("gate_rank"))
+
+
+@register_part("mixer", "wkv")
+def _build_wkv(spec, runtime, **_):
+    return Wkv(spec["hidden_size"], spec["num_heads"], spec["head_dim"], spec["norm_eps"], runtime,
+               decay_rank=spec.get("decay_rank"))

@@ -85,21 +85,24 @@ def _cast_error(exact: torch.Tensor, cast: torch.Tensor) -> tuple[int, float, fl
 
 
 def load_weights(folder, expected: Mapping[str, WeightSpec], engine_dtype: torch.dtype, device,
-                 aliases: Mapping[str, str] | None = None, report: dict | None = None) -> dict[str, torch.Tensor]:
+                 aliases: Mapping[str, str] | None = None, report: dict | None = None,
+                 optional=()) -> dict[str, torch.Tensor]:
     """``aliases``: name -> name of an expected tensor it must equal if the file
-    stores it (the tied head); such names are not "unexpected".  ``report``: a dict
+    stores it (the tied head); such names are not "unexpected".  ``optional``: names the
+    file may hold although the model reads none of them.  ``report``: a dict
     that receives what the cast to the engine's element types cost."""
     folder = Path(folder)
     handles, where = _open_files(folder)
     aliases = dict(aliases or {})
 
     missing = sorted(n for n in expected if n not in where)
-    unexpected = sorted(n for n in where if n not in expected and n not in aliases)
+    optional = set(optional)
+    unexpected = sorted(n for n in where if n not in expected and n not in aliases and n not in optional)
     wrong = []
     for name, spec in expected.items():
         if name in where:
             shape = tuple(handles[where[name]].get_slice(name).get_shape())
-            if shape != tuple(spec.shape):
+            if not spec.fits(shape):
                 wrong.append(f"{name}: file has {list(shape)}, model needs {list(spec.shape)}")
     if missing or unexpected or wrong:
         parts = [f"{folder}: the tensors do not match the model"]

@@ -25,6 +25,9 @@ def random_tensors(expected, seed: int, dtype, init_std: float = 0.02, gain_std:
     out = {}
     for name in sorted(expected):
         spec = expected[name]
+        if any(extent < 0 for extent in spec.shape):
+            raise ValueError(f"{name}: the configuration leaves an extent open ({list(spec.shape)}); random weights "
+                             "need every size (give the rank in the configuration)")
         if torch.device(device).type == "cuda":
             # a per-tensor seed drawn from the CPU generator keeps the order of names decisive
             s = int(torch.randint(0, 2 ** 62, (1,), generator=gen).item())
