@@ -29,6 +29,10 @@ copy of its tree under baseline/_ref (its stock ``Qwen3`` and ``Scheduler``,
 Triton kernels, float16) on the same workload and prints the same line.
 ``--workload mixed`` runs a continuous batch of 64 requests with prompts of 64
 to 2,048 tokens and 128 decoded tokens each through the entry point.
+``--workload designs`` times a prefill of 2,048 tokens and decode steps at batch 8 of the
+Sevipel design (windowed attention, gated delta rule, wkv rule, routed experts) at two sizes
+beside Qwen3 layers of equal width, depth and active feed-forward weights, and every kernel
+of an unrecorded step of each with its fraction of the measured peaks.
 """
 
 from __future__ import annotations
@@ -517,6 +521,172 @@ def run_mixed(args):
 
 
 # ---------------------------------------------------------------------------
+# two designs side by side
+# ---------------------------------------------------------------------------
+
+DESIGN_SIZES = {
+    "w1024": {"width": 1024, "heads": 8, "kv_heads": 4, "wkv_heads": 16, "experts": 16, "top": 2, "ff": 768,
+              "rank": 64, "window": 1024},
+    "w2048": {"width": 2048, "heads": 16, "kv_heads": 4, "wkv_heads": 32, "experts": 32, "top": 4, "ff": 768,
+              "rank": 64, "window": 1024},
+}
+DESIGN_LAYERS, DESIGN_VOCAB, DESIGN_CONTEXT = 8, 32768, 2048
+
+
+def design_configs(z):
+    """(Sevipel configuration, Qwen3 configuration) of one size: the same width, depth, head counts
+    and head size; the dense feed-forward has as many weights as a token's chosen experts."""
+    mlp = {"kind": "moe", "expert": {"ff": z["ff"]}, "router": {"experts": z["experts"], "top": z["top"]}}
+    att = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+           "mask": {"size": z["window"]}, "rot": {"dims": 64, "base": 1000000.0}}
+    delta = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": 128, "vdim": 128, "conv": 4,
+             "decay_rank": z["rank"], "gate_rank": z["rank"]}
+    wkv = {"heads": z["wkv_heads"], "dim": 64, "decay_rank": z["rank"]}
+    kinds = [("attention", att), ("channel_delta", delta), ("channel_delta", delta), ("wkv", wkv),
+             ("attention", dict(att, kv_from=0)), ("channel_delta", delta), ("channel_delta", delta), ("wkv", wkv)]
+    sevipel = {"architecture": "Sevipel", "vocab": DESIGN_VOCAB, "width": z["width"], "norm": {"eps": 1e-5},
+               "max_positions": 4096,
+               "layers": [{"type": t, "mixer": dict(m), "mlp": mlp} for t, m in kinds[:DESIGN_LAYERS]]}
+    qwen = dict(QWEN3_0_6B, num_hidden_layers=DESIGN_LAYERS, hidden_size=z["width"], num_attention_heads=z["heads"],
+                num_key_value_heads=z["kv_heads"], head_dim=128, vocab_size=DESIGN_VOCAB,
+                intermediate_size=-(-2 * z["top"] * z["ff"] // 3 // 128) * 128, max_position_embeddings=4096)
+    return sevipel, qwen
+
+
+def kernel_times(runner, entries_of, steps=3):
+    """Milliseconds a step spends in each kernel face, from CUDA events around every launch of
+    unrecorded steps (the last `steps` of `steps + 2`); and the launches a step makes."""
+    import torch
+
+    from lockstep_b200 import kernels as K
+
+    faces = ["embed_gather", "rmsnorm", "qk_norm_rope_store", "gemm_nt_tc", "gemm_nt_simt", "gemm_nt_tc_rmsnorm",
+             "gemm_nt_tc_qkv_heads", "attention_tile", "attention_decode", "attention_decode_mma",
+             "attention_prefill_tc", "attention_combine", "qkv_finish", "find_portions", "delta_prep", "shift_mix",
+             "lowrank_decay", "state_rule", "head_rms_gate", "experts_route", "experts_plan", "experts_product",
+             "experts_combine"]
+    records, saved, graphs = [], {}, runner.graphs
+    runner.graphs = None
+
+    def wrap(name, fn):
+        def timed(*a, **kw):
+            label = name
+            if name == "state_rule":
+                label = "delta_rule" if a[0] == K.RULE_DELTA else "wkv_rule"
+            elif name == "experts_product":
+                label = "experts_up" if a[0] == 0 else "experts_down"
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            out = fn(*a, **kw)
+            e1.record()
+            records.append((label, e0, e1))
+            return out
+        return timed
+
+    for name in faces:
+        saved[name] = getattr(K, name)
+        setattr(K, name, wrap(name, saved[name]))
+    try:
+        out: dict[str, float] = {}
+        for r in range(steps + 2):
+            records.clear()
+            close = entries_of(r)
+            torch.cuda.synchronize()
+            if r >= 2:
+                for label, e0, e1 in records:
+                    out[label] = out.get(label, 0.0) + e0.elapsed_time(e1) / steps
+            close()
+        launches = len(records)
+    finally:
+        for name, fn in saved.items():
+            setattr(K, name, fn)
+        runner.graphs = graphs
+    return {k: round(v, 4) for k, v in sorted(out.items(), key=lambda kv: -kv[1])}, launches
+
+
+def run_designs(args):
+    import torch
+
+    from lockstep_b200 import StepEntry
+
+    pk = peaks()
+    tokens, batch, context = PREFILL_TOKENS, 8, DESIGN_CONTEXT
+    sizes = {}
+    clocks = ClockSampler()
+    clocks.start()
+    for size, z in DESIGN_SIZES.items():
+        sevipel, qwen = design_configs(z)
+        row = {}
+        for design, cfg in (("sevipel", sevipel), ("qwen3", qwen)):
+            engine = build_engine(cfg, "bfloat16", batch, context + 64)
+            runner = engine.runner
+            prefill = time_prefill(runner, tokens)
+            steps = 100
+            decode = time_decode(runner, engine.sampler, batch, context, steps, args.warmup, repeats=3)
+            ids = [(5 * i + 3) % 1000 for i in range(tokens)]
+
+            def prefill_step(r):
+                runner.open(f"k{r}")
+                runner.step([StepEntry(uid=f"k{r}", tokens=ids, start=0, want=[tokens - 1])], check=False)
+                return lambda: runner.close(f"k{r}")
+
+            def decode_step(r):
+                uids = [f"q{r}_{i}" for i in range(batch)]
+                for u in uids:
+                    runner.open(u)
+                    runner.fill_random(u, context - 1)
+                runner.step([StepEntry(uid=u, tokens=[7], start=context - 1, want=[0]) for u in uids], check=False)
+                return lambda: [runner.close(u) for u in uids]
+
+            p_kernels, p_launches = kernel_times(runner, prefill_step)
+            d_kernels, d_launches = kernel_times(runner, decode_step)
+            p_ms, d_ms = statistics.median(prefill), statistics.median(decode)
+            row[design] = {
+                "prefill_ms": round(p_ms, 3), "prefill_tok_s": round(tokens / p_ms * 1e3, 1),
+                "decode_ms_per_step": round(d_ms, 4), "decode_tok_s": round(batch / d_ms * 1e3, 1),
+                "prefill_kernels_ms": p_kernels, "prefill_launches": p_launches,
+                "decode_kernels_ms": d_kernels, "decode_launches": d_launches,
+            }
+            del engine, runner
+            torch.cuda.empty_cache()
+        # the kernels of the two designs that do like work, each against its own roof
+        w, ff, top, layers = z["width"], z["ff"], z["top"], DESIGN_LAYERS
+        s, q = row["sevipel"], row["qwen3"]
+        flops_experts = 2 * tokens * top * ff * w * layers          # one of the two products, all layers
+        qw = qwen
+        flops_dense = 2 * tokens * layers * ((qw["num_attention_heads"] + 2 * qw["num_key_value_heads"]) * 128 * w
+                                             + qw["num_attention_heads"] * 128 * w + 3 * qw["intermediate_size"] * w) \
+            + 2 * DESIGN_VOCAB * w
+        state_bytes = 2 * 4 * batch * (4 * z["heads"] * 128 * 128 + 2 * z["wkv_heads"] * 64 * 64)   # read and written, all layers
+        cache_bytes = 2 * batch * layers * context * 2 * z["kv_heads"] * 128
+
+        def frac(amount, ms, peak):
+            return round(amount / (ms * 1e-3) / peak, 4) if ms else None
+
+        like = {
+            "prefill: experts_up (tensor cores asked for) vs qwen3 products": [
+                frac(flops_experts, s["prefill_kernels_ms"].get("experts_up"), pk["bf16_tflops"] * 1e12),
+                frac(flops_dense, q["prefill_kernels_ms"].get("gemm_nt_tc"), pk["bf16_tflops"] * 1e12)],
+            "prefill: experts_down vs qwen3 products": [
+                frac(flops_experts, s["prefill_kernels_ms"].get("experts_down"), pk["bf16_tflops"] * 1e12),
+                frac(flops_dense, q["prefill_kernels_ms"].get("gemm_nt_tc"), pk["bf16_tflops"] * 1e12)],
+            "decode: state rules (bytes of state) vs qwen3 decode attention (bytes of cache)": [
+                frac(state_bytes, s["decode_kernels_ms"].get("delta_rule", 0) + s["decode_kernels_ms"].get("wkv_rule", 0),
+                     pk["hbm_gbs"] * 1e9),
+                frac(cache_bytes, q["decode_kernels_ms"].get("attention_decode_mma"), pk["hbm_gbs"] * 1e9)],
+        }
+        row["like_kernels_fraction_of_measured_peak [sevipel, qwen3]"] = like
+        sizes[size] = row
+    clock = clocks.stop()
+    print(json.dumps({
+        "metric": "prefill of 2,048 tokens and decode at batch 8, context 2,048: Sevipel beside Qwen3 layers of equal size",
+        "unit": "ms, tok/s", "n_gpus": 1, "dtype": "bf16", "data": "synthetic", "impl": "ours", "clocks": clock,
+        "peaks": pk, "layers": DESIGN_LAYERS, "vocab": DESIGN_VOCAB, "sizes": sizes,
+    }))
+    return 0
+
+
+# ---------------------------------------------------------------------------
 # the reference arm: LockStep itself, unmodified, from baseline/_ref
 # ---------------------------------------------------------------------------
 
@@ -685,8 +855,9 @@ def main():
     ap.add_argument("--no-fp32", action="store_true", help="skip the float32 points")
     ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
                     help="time only this part and print a short line (for profiling a small case)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "mixed"],
-                    help="mixed: a continuous batch of 64 requests through the entry point")
+    ap.add_argument("--workload", default="decode", choices=["decode", "mixed", "designs"],
+                    help="mixed: a continuous batch of 64 requests through the entry point; designs: the Sevipel "
+                         "design beside Qwen3 layers of equal size, with every kernel's time")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"],
                     help="element type of the --only runs (the full line always reports both)")
     ap.add_argument("--context", type=int, default=CONTEXT, help="context length of the decode steps (--only decode)")
@@ -702,6 +873,8 @@ def main():
         return run_reference(args)
     if args.workload == "mixed":
         return run_mixed(args)
+    if args.workload == "designs":
+        return run_designs(args)
     return run_ours(args)
 
 

@@ -17,7 +17,7 @@ import json
 _SOURCES = {
     "core": ["attention_simt", "gemm_simt", "sampling"],
     "tc": ["gemm_tc", "attention_decode_mma", "attention_prefill_tc"],
-    "seq": ["recurrent", "experts"],
+    "seq": ["recurrent", "experts", "experts_tc"],
 }
 
 

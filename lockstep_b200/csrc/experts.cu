@@ -61,8 +61,9 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) route_kernel(const float* __
 // plan [0] = tiles, then (expert, first row, rows) per tile; row_token / row_weight per sorted
 // row; pair_row [T * top]: the sorted row of a pair
 __global__ void __launch_bounds__(PLAN_THREADS) plan_kernel(const int* __restrict__ ids, const float* __restrict__ weights,
-                                                            int pairs, int top, int experts, int* __restrict__ plan,
-                                                            int max_tiles, int* __restrict__ row_token,
+                                                            int pairs, int top, int experts, int tile_rows,
+                                                            int* __restrict__ plan, int max_tiles,
+                                                            int* __restrict__ row_token,
                                                             float* __restrict__ row_weight, int* __restrict__ pair_row,
                                                             int* err) {
   extern __shared__ int sm[];
@@ -82,11 +83,11 @@ __global__ void __launch_bounds__(PLAN_THREADS) plan_kernel(const int* __restric
     int at = 0, tiles = 0;
     for (int e = 0; e < experts; ++e) {
       first[e] = at;
-      for (int r0 = 0; r0 < count[e]; r0 += TILE_M) {
+      for (int r0 = 0; r0 < count[e]; r0 += tile_rows) {
         if (tiles < max_tiles) {
           plan[1 + 3 * tiles] = e;
           plan[1 + 3 * tiles + 1] = at + r0;
-          plan[1 + 3 * tiles + 2] = count[e] - r0 < TILE_M ? count[e] - r0 : TILE_M;
+          plan[1 + 3 * tiles + 2] = count[e] - r0 < tile_rows ? count[e] - r0 : tile_rows;
         }
         ++tiles;
       }
@@ -212,14 +213,16 @@ LS_API int ls_experts_route(const float* logits, int tokens, int experts, int to
   return ls_launch_status();
 }
 
-LS_API int ls_experts_plan(const int* ids, const float* weights, int tokens, int top, int experts, int* plan,
-                           int max_tiles, int* row_token, float* row_weight, int* pair_row, int* err,
+// tile_rows: the most rows of a tile (what the product that reads the plan takes: ls_experts_tile_rows()
+// for the CUDA-core product, the tensor-core product's own)
+LS_API int ls_experts_plan(const int* ids, const float* weights, int tokens, int top, int experts, int tile_rows,
+                           int* plan, int max_tiles, int* row_token, float* row_weight, int* pair_row, int* err,
                            cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (experts <= 0 || experts > 4096 || top <= 0 || max_tiles <= 0) return LS_E_SIZE;
+  if (experts <= 0 || experts > 4096 || top <= 0 || max_tiles <= 0 || tile_rows <= 0) return LS_E_SIZE;
   LS_COUNT(LS_K_EXPERTS_PLAN);
   cudaError_t e = ls_launch(plan_kernel, dim3(1), dim3(PLAN_THREADS), sizeof(int) * 3 * (size_t)experts, stream, ids,
-                            weights, tokens * top, top, experts, plan, max_tiles, row_token, row_weight, pair_row, err);
+                            weights, tokens * top, top, experts, tile_rows, plan, max_tiles, row_token, row_weight, pair_row, err);
   if (e != cudaSuccess) return (int)e;
   return ls_launch_status();
 }
@@ -229,7 +232,7 @@ LS_API int ls_experts_plan(const int* ids, const float* weights, int tokens, int
 LS_API int ls_experts_product(int mode, int dtype, const int* plan, int max_tiles, const void* A, const int* row_token,
                               const float* row_weight, const void* W, void* C, int N, int K, cudaStream_t stream) {
   if (max_tiles <= 0) return 0;
-  if (N <= 0 || K <= 0 || max_tiles > 65535) return LS_E_SIZE;
+  if (N <= 0 || K <= 0 || max_tiles > 65535) return LS_E_SIZE;     // (the plan's tiles hold up to TILE_M rows)
   const dim3 grid((N + TILE_N - 1) / TILE_N, max_tiles);
   LS_COUNT(mode == 0 ? LS_K_EXPERTS_UP : LS_K_EXPERTS_DOWN);
   cudaError_t e;

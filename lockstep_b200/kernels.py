@@ -105,8 +105,12 @@ _SIGNATURES["seq"] = {
                          c_float, c_void_p],
     "ls_experts_tile_rows": [],
     "ls_experts_route": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
-    "ls_experts_plan": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+    "ls_experts_plan": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                         c_void_p, c_void_p],
+    "ls_experts_tc_tile_rows": [],
+    "ls_experts_gather": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "ls_experts_product_tc": [c_int, c_void_p, c_int, c_void_p, ctypes.c_longlong, c_void_p, c_int, c_void_p, c_int,
+                              c_int, c_void_p, c_void_p],
     "ls_experts_product": [c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                            c_int, c_void_p],
     "ls_experts_combine": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -658,8 +662,11 @@ def head_rms_gate(o, gain, gate_f32, gate_x, out, heads: int, dv: int, gain_shar
         1 if gain_shared else 0, float(eps), _stream()), "head_rms_gate")
 
 
-def experts_tile_rows() -> int:
-    return int(library("seq").ls_experts_tile_rows())
+def experts_tile_rows(tensor_cores: bool = False) -> int:
+    """The most rows of a tile of the experts' products: of the CUDA-core product, or of the
+    tensor-core one."""
+    lib = library("seq")
+    return int(lib.ls_experts_tc_tile_rows() if tensor_cores else lib.ls_experts_tile_rows())
 
 
 def experts_route(logits, top: int, ids, weights) -> None:
@@ -669,10 +676,11 @@ def experts_route(logits, top: int, ids, weights) -> None:
                                            _stream()), "experts_route")
 
 
-def experts_plan(ids, weights, experts: int, plan, max_tiles: int, row_token, row_weight, pair_row, err) -> None:
+def experts_plan(ids, weights, experts: int, tile_rows: int, plan, max_tiles: int, row_token, row_weight, pair_row,
+                 err) -> None:
     tokens, top = ids.shape
     _check(library("seq").ls_experts_plan(
-        _dev(ids, "ids", torch.int32), _dev(weights, "weights", torch.float32), tokens, top, experts,
+        _dev(ids, "ids", torch.int32), _dev(weights, "weights", torch.float32), tokens, top, experts, tile_rows,
         _dev(plan, "plan", torch.int32), max_tiles, _dev(row_token, "row_token", torch.int32),
         _dev(row_weight, "row_weight", torch.float32), _dev(pair_row, "pair_row", torch.int32),
         _dev(err, "err", torch.int32), _stream()), "experts_plan")
@@ -695,3 +703,32 @@ def experts_combine(y, pair_row, residual, top: int) -> None:
     _check(library("seq").ls_experts_combine(_dev(y, "y", torch.float32), _dev(pair_row, "pair_row", torch.int32),
                                              _dev(residual, "residual", torch.float32), tokens, top, width, _stream()),
            "experts_combine")
+
+
+def experts_gather(x, row_token, row_weight, out) -> None:
+    """out[row] = x[row_token[row]] * row_weight[row] (bfloat16): the sorted, scaled rows that the
+    tensor-core product of the experts' first matrices reads."""
+    rows, width = out.shape
+    if x.shape[1] != width or x.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("experts_gather: shapes or types do not agree")
+    _check(library("seq").ls_experts_gather(_dev(x, "x"), _dev(row_token, "row_token", torch.int32),
+                                            _dev(row_weight, "row_weight", torch.float32), _dev(out, "out"), rows,
+                                            width, _stream()), "experts_gather")
+
+
+def experts_product_tc(mode: int, plan, max_tiles: int, a, w, c, err) -> bool:
+    """The experts' product on tcgen05 (csrc/experts_tc.cu): a [rows, k] bfloat16 sorted by expert, w
+    [experts, n, k] bfloat16; mode 0: c = relu(a @ w[e].T)^2 (bfloat16), mode 1: c = a @ w[e].T (float32).
+    Returns False, having launched nothing, for what TMA cannot address."""
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not USE_TENSOR_CORES[0]:
+        return False
+    n, k = w.shape[1], w.shape[2]
+    if a.shape[1] != k or c.shape != (a.shape[0], n) or c.dtype != (torch.bfloat16 if mode == 0 else torch.float32):
+        raise KernelError("experts_product_tc: shapes or types do not agree")
+    status = library("seq").ls_experts_product_tc(
+        mode, _dev(plan, "plan", torch.int32), max_tiles, _dev(a, "a"), a.shape[0], _dev(w, "w"), w.shape[0],
+        _dev(c, "c"), n, k, _dev(err, "err", torch.int32), _stream())
+    if status in (-2, -3):
+        return False
+    _check(status, "experts_product_tc")
+    return True

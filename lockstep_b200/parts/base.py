@@ -29,6 +29,9 @@ class WeightSpec:
 
     shape: tuple[int, ...]
     role: str = "matrix"
+    # how the random-weights mode draws the tensor where the role's default does not suit it:
+    # ("normal", mean, std) or ("uniform", low, high)
+    init: tuple | None = None
 
     def fits(self, shape) -> bool:
         shape = tuple(shape)

@@ -54,17 +54,26 @@ class RoutedExperts(FeedForward):
         ids = rt.rows(tokens, self.top, dtype=i32)
         weights = rt.rows(tokens, self.top, dtype=f32)
         K.experts_route(logits, self.top, ids, weights)
-        tile = K.experts_tile_rows()
+        # bfloat16 products go to the tensor cores where TMA can address the rows (16-byte pitches)
+        tensor_cores = (rt.dtype == torch.bfloat16 and K.USE_TENSOR_CORES[0] and self.h % 8 == 0 and self.f % 8 == 0)
+        tile = K.experts_tile_rows(tensor_cores)
         max_tiles = min(pairs, pairs // tile + self.E)
         plan = rt.rows(1 + 3 * max_tiles, dtype=i32)
         row_token = rt.rows(pairs, dtype=i32)
         row_weight = rt.rows(pairs, dtype=f32)
         pair_row = rt.rows(pairs, dtype=i32)
-        K.experts_plan(ids, weights, self.E, plan, max_tiles, row_token, row_weight, pair_row, rt.err)
+        K.experts_plan(ids, weights, self.E, tile, plan, max_tiles, row_token, row_weight, pair_row, rt.err)
         act = rt.rows(pairs, self.f)
-        K.experts_product(0, plan, max_tiles, x, row_token, row_weight, self.w_up, act)
         y = rt.rows(pairs, self.h, dtype=f32)
-        K.experts_product(1, plan, max_tiles, act, row_token, row_weight, self.w_down, y)
+        if tensor_cores:
+            scaled = rt.rows(pairs, self.h)
+            K.experts_gather(x, row_token, row_weight, scaled)
+            if not (K.experts_product_tc(0, plan, max_tiles, scaled, self.w_up, act, rt.err)
+                    and K.experts_product_tc(1, plan, max_tiles, act, self.w_down, y, rt.err)):
+                raise K.KernelError("routed_experts: the tensor-core product refused shapes it was chosen for")
+        else:
+            K.experts_product(0, plan, max_tiles, x, row_token, row_weight, self.w_up, act)
+            K.experts_product(1, plan, max_tiles, act, row_token, row_weight, self.w_down, y)
         K.experts_combine(y, pair_row, residual, self.top)
 
 

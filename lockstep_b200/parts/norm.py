@@ -48,7 +48,7 @@ class RMSNorm(Norm):
         self.gain: torch.Tensor | None = None
 
     def weight_specs(self):
-        return {self.tensor: WeightSpec((self.width,), "gain")}
+        return {self.tensor: WeightSpec((self.width,), "gain", ("normal", 0.0, 0.1) if self.offset else None)}
 
     def bind(self, tensors):
         self.gain = tensors[self.tensor]

@@ -70,14 +70,15 @@ class GatedDelta(Mixer):
                          state_dtype=torch.float32)
 
     def weight_specs(self):
+        taps = ("normal", 0.0, 0.5)
         return {
             "q": WeightSpec((self.Kd, self.w)), "k": WeightSpec((self.Kd, self.w)), "v": WeightSpec((self.Vd, self.w)),
-            "q.conv": WeightSpec((self.Kd, self.taps), "gain"), "k.conv": WeightSpec((self.Kd, self.taps), "gain"),
-            "v.conv": WeightSpec((self.Vd, self.taps), "gain"),
-            "b": WeightSpec((self.H, self.w)), "A_log": WeightSpec((self.H,), "gain"),
+            "q.conv": WeightSpec((self.Kd, self.taps), "gain", taps), "k.conv": WeightSpec((self.Kd, self.taps), "gain", taps),
+            "v.conv": WeightSpec((self.Vd, self.taps), "gain", taps),
+            "b": WeightSpec((self.H, self.w)), "A_log": WeightSpec((self.H,), "gain", ("normal", -1.0, 0.5)),
             "norm": WeightSpec((self.dv,), "gain"),
             "a1": WeightSpec((self.rank_a, self.w)), "a2": WeightSpec((self.H * self.dk, self.rank_a)),
-            "dt_bias": WeightSpec((self.H * self.dk,), "gain"),
+            "dt_bias": WeightSpec((self.H * self.dk,), "gain", ("normal", -1.0, 1.0)),
             "g1": WeightSpec((self.rank_g, self.w)), "g2": WeightSpec((self.Vd, self.rank_g)),
             "o": WeightSpec((self.w, self.Vd)),
         }
@@ -127,12 +128,13 @@ class Wkv(Mixer):
         return CacheNeed("state", state_shape=(self.H * self.d * self.d + self.w,), state_dtype=torch.float32)
 
     def weight_specs(self):
-        specs = {f"mu.{s}": WeightSpec((self.w,), "gain") for s in self.MIXES}
+        specs = {f"mu.{s}": WeightSpec((self.w,), "gain", ("uniform", 0.0, 1.0)) for s in self.MIXES}
         specs.update({
             "r": WeightSpec((self.A, self.w)), "k": WeightSpec((self.A, self.w)), "v": WeightSpec((self.A, self.w)),
             "g": WeightSpec((self.A, self.w)), "w1": WeightSpec((self.rank, self.w)),
             "w2": WeightSpec((self.A, self.rank)),
-            "w0": WeightSpec((self.A,), "gain"), "u": WeightSpec((self.H, self.d), "gain"),
+            "w0": WeightSpec((self.A,), "gain", ("normal", -2.5, 1.0)),
+            "u": WeightSpec((self.H, self.d), "gain", ("normal", 0.0, 0.5)),
             "norm": WeightSpec((self.A,), "gain"), "o": WeightSpec((self.w, self.A)),
         })
         return specs

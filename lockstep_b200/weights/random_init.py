@@ -3,7 +3,8 @@ model.safetensors) from a configuration and a seed.
 
 Tensors are drawn in the order of their sorted names from one seeded CPU
 generator, so a (configuration, seed, dtype) names one model.  Matrices and
-tables are N(0, init_std), norm gains 1 + N(0, gain_std).
+tables are N(0, init_std), norm gains 1 + N(0, gain_std); a part may give a tensor a
+distribution of its own (``WeightSpec.init``: a gain stored around zero, a decay's bias).
 """
 
 from __future__ import annotations
@@ -35,7 +36,15 @@ def random_tensors(expected, seed: int, dtype, init_std: float = 0.02, gain_std:
             t = torch.randn(spec.shape, generator=g, dtype=torch.float32, device=device)
         else:
             t = torch.randn(spec.shape, generator=gen, dtype=torch.float32)
-        t = 1.0 + gain_std * t if spec.role == "gain" else init_std * t
+        if spec.init is not None and spec.init[0] == "normal":
+            t = spec.init[1] + spec.init[2] * t
+        elif spec.init is not None and spec.init[0] == "uniform":
+            # (the normal draw keeps the generator's order; its distribution function makes it uniform)
+            t = spec.init[1] + (spec.init[2] - spec.init[1]) * (0.5 * (1.0 + torch.erf(t / 2.0 ** 0.5)))
+        elif spec.init is not None:
+            raise ValueError(f"{name}: unknown initialisation {spec.init!r}")
+        else:
+            t = 1.0 + gain_std * t if spec.role == "gain" else init_std * t
         out[name] = t.to(dtype).contiguous()
     return out
 
