@@ -563,8 +563,8 @@ def kernel_times(runner, entries_of, steps=3):
     faces = ["embed_gather", "rmsnorm", "qk_norm_rope_store", "gemm_nt_tc", "gemm_nt_simt", "gemm_nt_tc_rmsnorm",
              "gemm_nt_tc_qkv_heads", "attention_tile", "attention_decode", "attention_decode_mma",
              "attention_prefill_tc", "attention_combine", "qkv_finish", "find_portions", "delta_prep", "shift_mix",
-             "lowrank_decay", "state_rule", "head_rms_gate", "experts_route", "experts_plan", "experts_product",
-             "experts_combine"]
+             "tanh_rows", "double_exp_decay", "state_rule", "head_rms_gate", "experts_route", "experts_plan", "experts_product",
+             "experts_product_tc", "experts_gather", "experts_combine"]
     records, saved, graphs = [], {}, runner.graphs
     runner.graphs = None
 
@@ -573,7 +573,7 @@ def kernel_times(runner, entries_of, steps=3):
             label = name
             if name == "state_rule":
                 label = "delta_rule" if a[0] == K.RULE_DELTA else "wkv_rule"
-            elif name == "experts_product":
+            elif name in ("experts_product", "experts_product_tc"):
                 label = "experts_up" if a[0] == 0 else "experts_down"
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()

@@ -68,17 +68,18 @@ enum LsKernelId {
   LS_K_SAMPLE, LS_K_GEMM_TC_FEW, LS_K_GEMM_TC_FEW_NORM, LS_K_GEMM_TC_FEW_QKV, LS_K_GEMM_TC_CLUSTER,
   LS_K_GEMM_TC_WALK, LS_K_GEMM_TC_ROWS, LS_K_GEMM_TC_ROWS_PAIR, LS_K_ATTENTION_DECODE_MMA,
   LS_K_ATTENTION_PREFILL_TC, LS_K_GEMM_SIMT_FEW, LS_K_GEMM_SIMT_MANY, LS_K_QKV_FINISH, LS_K_FIND_PORTIONS,
-  LS_K_DELTA_PREP, LS_K_SHIFT_MIX, LS_K_LOWRANK_DECAY, LS_K_DELTA_RULE, LS_K_WKV_RULE, LS_K_HEAD_RMS_GATE,
+  LS_K_DELTA_PREP, LS_K_SHIFT_MIX, LS_K_DELTA_RULE, LS_K_WKV_RULE, LS_K_HEAD_RMS_GATE,
   LS_K_EXPERTS_ROUTE, LS_K_EXPERTS_PLAN, LS_K_EXPERTS_UP, LS_K_EXPERTS_DOWN, LS_K_EXPERTS_COMBINE,
-  LS_K_EXPERTS_GATHER, LS_K_EXPERTS_UP_TC, LS_K_EXPERTS_DOWN_TC, LS_K_COUNT
+  LS_K_EXPERTS_GATHER, LS_K_EXPERTS_UP_TC, LS_K_EXPERTS_DOWN_TC, LS_K_TANH, LS_K_DOUBLE_EXP_DECAY,
+  LS_K_COUNT
 };
 #define LS_KERNEL_NAMES                                                                                  \
   "embed_gather,rmsnorm,qk_norm_rope_store,qk_norm_rope_store_whole,silu_mul,gemm_simt,attention_tile," \
   "attention_decode,attention_combine,argmax,sample,gemm_tc_few,gemm_tc_few_norm,gemm_tc_few_qkv,"      \
   "gemm_tc_cluster,gemm_tc_walk,gemm_tc_rows,gemm_tc_rows_pair,attention_decode_mma,attention_prefill_tc,"     \
-  "gemm_simt_few,gemm_simt_many,qkv_finish,find_portions,delta_prep,shift_mix,lowrank_decay,delta_rule,"       \
+  "gemm_simt_few,gemm_simt_many,qkv_finish,find_portions,delta_prep,shift_mix,delta_rule,"       \
   "wkv_rule,head_rms_gate,experts_route,experts_plan,experts_up,experts_down,experts_combine,"     \
-  "experts_gather,experts_up_tc,experts_down_tc"
+  "experts_gather,experts_up_tc,experts_down_tc,tanh_rows,double_exp_decay"
 // one table per library: hidden, so that two libraries loaded into one process do not share it
 __attribute__((visibility("hidden"))) inline unsigned long long ls_kernel_launches[LS_K_COUNT];
 #define LS_COUNT(id) (++ls_kernel_launches[id])

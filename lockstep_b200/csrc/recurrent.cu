@@ -103,21 +103,18 @@ constexpr int PREP_THREADS = 256;
 constexpr int MAX_TAPS = 8;
 
 struct DeltaPrepArgs {
-  const void* proj;        // [T, ld]: q (G dk) | k (G dk) | v (H dv) | beta (H) | a1 (Ra) | g1 (Rg)
+  const void* proj;        // [T, ld]: q (G dk) | k (G dk) | v (H dv) | beta (H) | ...
   int64_t ld;
   const float* conv_w;     // [C, taps], C = 2 G dk + H dv; the last tap is the current token's
-  const void* w_a2;        // [H dk, Ra]
   const float* dt_bias;    // [H dk]
   const float* a_log;      // [H]
-  const void* w_g2;        // [H dv, Rg]
   const float* state;      // per slot: S [H, dk, dv], then the last taps - 1 inputs of the convolution [taps - 1, C]
   int64_t state_stride;
   const int* token_slot;
   float* qkv;              // [T, C]: q (unit, scaled), k (unit), v, after convolution and silu
-  float* decay;            // [T, H dk]
+  float* decay;            // [T, H dk]: in, the output z of the decay's low-rank map; out, exp(-exp(A_log) softplus(z + dt_bias))
   float* beta;             // [T, H]
-  float* gate;             // [T, H dv]
-  int T, H, G, dk, dv, taps, Ra, Rg;
+  int T, H, G, dk, dv, taps;
   float unit_eps;
 };
 
@@ -128,9 +125,7 @@ __global__ void __launch_bounds__(PREP_THREADS) delta_prep_kernel(DeltaPrepArgs 
   const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int Kd = a.G * a.dk, Vd = a.H * a.dv, C = 2 * Kd + Vd;
   float* conv = smem;              // [C]
-  float* low_a = conv + C;         // [Ra]
-  float* low_g = low_a + a.Ra;     // [Rg]
-  float* head_scale = low_g + a.Rg;  // [2 G]
+  float* head_scale = conv + C;    // [2 G]
   const T* proj = reinterpret_cast<const T*>(a.proj);
   const T* row = proj + (int64_t)t * a.ld;
   const int slot = a.token_slot[t];
@@ -148,8 +143,6 @@ __global__ void __launch_bounds__(PREP_THREADS) delta_prep_kernel(DeltaPrepArgs 
     }
     conv[c] = silu_f(acc);
   }
-  for (int r = tid; r < a.Ra; r += PREP_THREADS) low_a[r] = ls_to_float<T>(row[C + a.H + r]);
-  for (int r = tid; r < a.Rg; r += PREP_THREADS) low_g[r] = ls_to_float<T>(row[C + a.H + a.Ra + r]);
   __syncthreads();
   // q and k heads to unit length; q also by dk^(-1/2)
   for (int h = warp; h < 2 * a.G; h += PREP_THREADS / 32) {
@@ -165,19 +158,17 @@ __global__ void __launch_bounds__(PREP_THREADS) delta_prep_kernel(DeltaPrepArgs 
   float* out = a.qkv + (int64_t)t * C;
   for (int c = tid; c < C; c += PREP_THREADS) out[c] = c < 2 * Kd ? conv[c] * head_scale[c / a.dk] : conv[c];
   for (int h = tid; h < a.H; h += PREP_THREADS) a.beta[(int64_t)t * a.H + h] = sigmoid_f(ls_to_float<T>(row[C + h]));
-  const T* w_a2 = reinterpret_cast<const T*>(a.w_a2);
-  for (int i = tid; i < a.H * a.dk; i += PREP_THREADS) {
-    float z = 0.f;
-    for (int r = 0; r < a.Ra; ++r) z = fmaf(ls_to_float<T>(w_a2[(int64_t)i * a.Ra + r]), low_a[r], z);
-    z += a.dt_bias[i];
-    a.decay[(int64_t)t * a.H * a.dk + i] = expf(-expf(a.a_log[i / a.dk]) * softplus_f(z));
-  }
-  const T* w_g2 = reinterpret_cast<const T*>(a.w_g2);
-  for (int i = tid; i < Vd; i += PREP_THREADS) {
-    float z = 0.f;
-    for (int r = 0; r < a.Rg; ++r) z = fmaf(ls_to_float<T>(w_g2[(int64_t)i * a.Rg + r]), low_g[r], z);
-    a.gate[(int64_t)t * Vd + i] = sigmoid_f(z);
-  }
+  float* decay = a.decay + (int64_t)t * a.H * a.dk;
+  for (int i = tid; i < a.H * a.dk; i += PREP_THREADS)
+    decay[i] = expf(-expf(a.a_log[i / a.dk]) * softplus_f(decay[i] + a.dt_bias[i]));
+}
+
+// z <- exp(-exp(z + bias[column])), element by element: a decay from its low-rank map's output
+__global__ void __launch_bounds__(PREP_THREADS) double_exp_decay_kernel(float* __restrict__ z, const float* __restrict__ bias,
+                                                                        int64_t count, int channels) {
+  ls_dependency_sync();
+  const int64_t i = (int64_t)blockIdx.x * PREP_THREADS + threadIdx.x;
+  if (i < count) z[i] = expf(-expf(z[i] + bias[i % channels]));
 }
 
 // ---------------------------------------------------------------------------------------
@@ -202,27 +193,18 @@ __global__ void __launch_bounds__(PREP_THREADS) shift_mix_kernel(const T* __rest
   }
 }
 
-// decay[t, i] = exp(-exp(w2[i, :] . tanh(low[t, :]) + w0[i]))
+// x <- tanh(x), element by element
 template <typename T>
-__global__ void __launch_bounds__(PREP_THREADS) lowrank_decay_kernel(const T* __restrict__ low, const T* __restrict__ w2,
-                                                                     const float* __restrict__ w0, float* __restrict__ decay,
-                                                                     int channels, int rank) {
-  extern __shared__ float smem[];
+__global__ void __launch_bounds__(PREP_THREADS) tanh_kernel(T* __restrict__ x, int64_t count) {
   ls_dependency_sync();
-  const int t = blockIdx.x;
-  for (int r = threadIdx.x; r < rank; r += PREP_THREADS) smem[r] = tanhf(ls_to_float<T>(low[(int64_t)t * rank + r]));
-  __syncthreads();
-  for (int i = threadIdx.x; i < channels; i += PREP_THREADS) {
-    float z = 0.f;
-    for (int r = 0; r < rank; ++r) z = fmaf(ls_to_float<T>(w2[(int64_t)i * rank + r]), smem[r], z);
-    decay[(int64_t)t * channels + i] = expf(-expf(z + w0[i]));
-  }
+  const int64_t i = (int64_t)blockIdx.x * PREP_THREADS + threadIdx.x;
+  if (i < count) x[i] = ls_from_float<T>(tanhf(ls_to_float<T>(x[i])));
 }
 
 // ---------------------------------------------------------------------------------------
 // the recurrences
 // ---------------------------------------------------------------------------------------
-constexpr int ROWS = 32;          // key channels of a column that one thread keeps in registers
+constexpr int ROWS = 16;          // key channels of a column that one thread keeps in registers
 constexpr int CHUNK = 8;          // tokens staged in shared memory at a time
 enum { RULE_DELTA = 0, RULE_WKV = 1 };
 
@@ -235,7 +217,7 @@ struct RuleArgs {
   const void* in_a;        // delta: qkv; wkv: r
   const void* in_b;        // wkv: k
   const void* in_v;        // wkv: v
-  const float* decay;
+  const float* decay;      // [T, H dk]
   const float* beta;       // delta
   const float* bonus;      // wkv
   float* out;              // [T, H dv] float32
@@ -246,6 +228,15 @@ struct RuleArgs {
   int carry_rows;          // delta: taps - 1; wkv: 1
   int H, G, dk, dv, lanes; // lanes: threads that share a column (a power of two, lanes * ROWS >= dk)
 };
+
+// One staged value's source: where token t's copy lies (p + t * stride), and its element type.
+struct StageSrc {
+  const char* p;
+  int64_t stride;
+  int kind;                // 0: nothing (zero), 1: float32, 2: the engine's type
+};
+
+constexpr int STAGE_SLOTS = 4;     // staged values of a token that one thread fetches (more: the plain loader)
 
 template <int RULE, typename T>
 __global__ void __launch_bounds__(128) rule_kernel(RuleArgs a) {
@@ -261,6 +252,7 @@ __global__ void __launch_bounds__(128) rule_kernel(RuleArgs a) {
   const bool active = col < dv;
   const int g = h / (a.H / a.G);
   float* state = a.state + (int64_t)slot * a.state_stride + (int64_t)h * dk * dv;
+  // a thread keeps the key channels i = part * ROWS + r of its column
   float S[ROWS], bonus[ROWS];
 #pragma unroll
   for (int r = 0; r < ROWS; ++r) {
@@ -268,71 +260,187 @@ __global__ void __launch_bounds__(128) rule_kernel(RuleArgs a) {
     S[r] = (active && i < dk) ? state[(int64_t)i * dv + col] : 0.f;
     bonus[r] = (RULE == RULE_WKV && i < dk) ? a.bonus[h * dk + i] : 0.f;
   }
-  // staged per token: A [dk], B [dk], D [dk], V [CB], beta
+  // What is fetched per token: A [dk] (q or r), B [dk] (k), D [dk] (decay), V [CB], beta.
+  // In shared memory each of A, B, D lies as L runs of ROWS channels, a run padded by four
+  // words: the lanes that share a column read 16 bytes each from different banks, the lanes of
+  // other columns the same words.  Channels past dk stay zero (a zero key writes nothing).
   const int per_token = 3 * dk + CB + 1;
+  const int run = ROWS + 4, dkp = L * run, cbp = (CB + 3) & ~3;
+  const int stride = 3 * dkp + cbp + 4;              // words of a token in shared memory
   const int Kd = a.G * dk, C = 2 * Kd + a.H * dv;
-  for (int c0 = 0; c0 < n; c0 += CHUNK) {
-    const int cn = n - c0 < CHUNK ? n - c0 : CHUNK;
-    __syncthreads();
-    for (int e = tid; e < cn * per_token; e += blockDim.x) {
-      const int tt = e / per_token, k = e - tt * per_token;
-      const int64_t t = t0 + c0 + tt;
-      float v;
-      if (k < 3 * dk) {
-        const int which = k / dk, i = k - which * dk;
-        if (which == 2) v = a.decay[t * a.H * dk + h * dk + i];
-        else if (RULE == RULE_DELTA) v = reinterpret_cast<const float*>(a.in_a)[t * C + which * Kd + g * dk + i];
-        else v = ls_to_float<T>(reinterpret_cast<const T*>(which == 0 ? a.in_a : a.in_b)[t * a.H * dk + h * dk + i]);
-      } else if (k < 3 * dk + CB) {
-        const int j = col0 + (k - 3 * dk);
-        if (j >= dv) v = 0.f;
-        else if (RULE == RULE_DELTA) v = reinterpret_cast<const float*>(a.in_a)[t * C + 2 * Kd + h * dv + j];
-        else v = ls_to_float<T>(reinterpret_cast<const T*>(a.in_v)[t * a.H * dv + h * dv + j]);
-      } else {
-        v = RULE == RULE_DELTA ? a.beta[t * a.H + h] : 0.f;
-      }
-      smem[e] = v;
+  auto place = [&](int k) {                          // where fetched value k of a token lies
+    if (k < 3 * dk) {
+      const int which = k / dk, i = k - which * dk;
+      return which * dkp + (i / ROWS) * run + (i % ROWS);
     }
-    __syncthreads();
-    for (int tt = 0; tt < cn; ++tt) {
-      const float* A = smem + tt * per_token;
-      const float* B = A + dk;
-      const float* D = B + dk;
-      const float vj = D[dk + cl];
-      float o = 0.f;
-      if (RULE == RULE_DELTA) {
-        float dot = 0.f;
-#pragma unroll
-        for (int r = 0; r < ROWS; ++r) {
-          const int i = part * ROWS + r;
-          if (i < dk) {
-            S[r] *= D[i];
-            dot = fmaf(S[r], B[i], dot);
-          }
+    return k < 3 * dk + CB ? 3 * dkp + (k - 3 * dk) : 3 * dkp + cbp;
+  };
+  auto source = [&](int k) {
+    StageSrc s;
+    s.p = nullptr; s.stride = 0; s.kind = 0;
+    if (k >= per_token) return s;
+    if (k < 3 * dk) {
+      const int which = k / dk, i = k - which * dk;
+      if (which == 2) {
+        s.p = reinterpret_cast<const char*>(a.decay + h * dk + i);
+        s.stride = (int64_t)a.H * dk * 4;
+        s.kind = 1;
+      } else if (RULE == RULE_DELTA) {
+        s.p = reinterpret_cast<const char*>(reinterpret_cast<const float*>(a.in_a) + which * Kd + g * dk + i);
+        s.stride = (int64_t)C * 4;
+        s.kind = 1;
+      } else {
+        s.p = reinterpret_cast<const char*>(reinterpret_cast<const T*>(which == 0 ? a.in_a : a.in_b) + h * dk + i);
+        s.stride = (int64_t)a.H * dk * sizeof(T);
+        s.kind = 2;
+      }
+    } else if (k < 3 * dk + CB) {
+      const int j = col0 + (k - 3 * dk);
+      if (j < dv) {
+        if (RULE == RULE_DELTA) {
+          s.p = reinterpret_cast<const char*>(reinterpret_cast<const float*>(a.in_a) + 2 * Kd + h * dv + j);
+          s.stride = (int64_t)C * 4;
+          s.kind = 1;
+        } else {
+          s.p = reinterpret_cast<const char*>(reinterpret_cast<const T*>(a.in_v) + h * dv + j);
+          s.stride = (int64_t)a.H * dv * sizeof(T);
+          s.kind = 2;
         }
-        for (int off = L >> 1; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
-        const float u = D[dk + CB] * (vj - dot);
+      }
+    } else if (RULE == RULE_DELTA) {
+      s.p = reinterpret_cast<const char*>(a.beta + h);
+      s.stride = (int64_t)a.H * 4;
+      s.kind = 1;
+    }
+    return s;
+  };
+  auto fetch = [&](const StageSrc& s, int64_t t) {
+    if (s.kind == 0) return 0.f;
+    const char* at = s.p + t * s.stride;
+    if (s.kind == 2) return ls_to_float<T>(*reinterpret_cast<const T*>(at));
+    return *reinterpret_cast<const float*>(at);
+  };
+  auto walk = [&](const float* buf, int c0, int cn) {
+    for (int tt = 0; tt < cn; ++tt) {
+      const float* tok = buf + tt * stride;
+      const float4* A = reinterpret_cast<const float4*>(tok + part * run);
+      const float4* B = reinterpret_cast<const float4*>(tok + dkp + part * run);
+      const float4* D = reinterpret_cast<const float4*>(tok + 2 * dkp + part * run);
+      const float vj = tok[3 * dkp + cl];
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+      if (RULE == RULE_DELTA) {
+        float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+        float4 kk[ROWS / 4];
 #pragma unroll
-        for (int r = 0; r < ROWS; ++r) {
-          const int i = part * ROWS + r;
-          if (i < dk) {
-            S[r] = fmaf(B[i], u, S[r]);
-            o = fmaf(S[r], A[i], o);
-          }
+        for (int r = 0; r < ROWS / 4; ++r) {
+          const float4 dd = D[r];
+          kk[r] = B[r];
+          S[4 * r] *= dd.x; d0 = fmaf(S[4 * r], kk[r].x, d0);
+          S[4 * r + 1] *= dd.y; d1 = fmaf(S[4 * r + 1], kk[r].y, d1);
+          S[4 * r + 2] *= dd.z; d2 = fmaf(S[4 * r + 2], kk[r].z, d2);
+          S[4 * r + 3] *= dd.w; d3 = fmaf(S[4 * r + 3], kk[r].w, d3);
+        }
+        float dot = (d0 + d1) + (d2 + d3);
+        for (int off = L >> 1; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+        const float u = tok[3 * dkp + cbp] * (vj - dot);
+#pragma unroll
+        for (int r = 0; r < ROWS / 4; ++r) {
+          const float4 qq = A[r];
+          S[4 * r] = fmaf(kk[r].x, u, S[4 * r]); o0 = fmaf(S[4 * r], qq.x, o0);
+          S[4 * r + 1] = fmaf(kk[r].y, u, S[4 * r + 1]); o1 = fmaf(S[4 * r + 1], qq.y, o1);
+          S[4 * r + 2] = fmaf(kk[r].z, u, S[4 * r + 2]); o2 = fmaf(S[4 * r + 2], qq.z, o2);
+          S[4 * r + 3] = fmaf(kk[r].w, u, S[4 * r + 3]); o3 = fmaf(S[4 * r + 3], qq.w, o3);
         }
       } else {
 #pragma unroll
-        for (int r = 0; r < ROWS; ++r) {
-          const int i = part * ROWS + r;
-          if (i < dk) {
-            const float kv = B[i] * vj;
-            o = fmaf(A[i], fmaf(bonus[r], kv, S[r]), o);
-            S[r] = fmaf(D[i], S[r], kv);
-          }
+        for (int r = 0; r < ROWS / 4; ++r) {
+          const float4 rr = A[r], kk = B[r], dd = D[r];
+          float kv = kk.x * vj;
+          o0 = fmaf(rr.x, fmaf(bonus[4 * r], kv, S[4 * r]), o0); S[4 * r] = fmaf(dd.x, S[4 * r], kv);
+          kv = kk.y * vj;
+          o1 = fmaf(rr.y, fmaf(bonus[4 * r + 1], kv, S[4 * r + 1]), o1); S[4 * r + 1] = fmaf(dd.y, S[4 * r + 1], kv);
+          kv = kk.z * vj;
+          o2 = fmaf(rr.z, fmaf(bonus[4 * r + 2], kv, S[4 * r + 2]), o2); S[4 * r + 2] = fmaf(dd.z, S[4 * r + 2], kv);
+          kv = kk.w * vj;
+          o3 = fmaf(rr.w, fmaf(bonus[4 * r + 3], kv, S[4 * r + 3]), o3); S[4 * r + 3] = fmaf(dd.w, S[4 * r + 3], kv);
         }
       }
+      float o = (o0 + o1) + (o2 + o3);
       for (int off = L >> 1; off > 0; off >>= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
       if (active && part == 0) a.out[(int64_t)(t0 + c0 + tt) * a.H * dv + h * dv + col] = o;
+    }
+  };
+
+  for (int e = tid; e < 2 * CHUNK * stride; e += blockDim.x) smem[e] = 0.f;
+  __syncthreads();
+  if (per_token <= STAGE_SLOTS * (int)blockDim.x) {
+    // every thread fetches the same few values of every token: the next chunk's are on their way
+    // to registers while this chunk is walked, and go to the other buffer afterwards
+    StageSrc src[STAGE_SLOTS];
+    int at[STAGE_SLOTS];
+#pragma unroll
+    for (int m = 0; m < STAGE_SLOTS; ++m) {
+      const int k = tid + m * (int)blockDim.x;
+      src[m] = source(k);
+      at[m] = k < per_token ? place(k) : -1;
+    }
+    // The loads of a chunk are issued together, without a branch between them (a slot that
+    // fetches nothing reads a valid word and drops it; tokens past the portion's end read its
+    // last token again); what they brought is converted when it goes to shared memory.
+    const char* from[STAGE_SLOTS];
+    bool half[STAGE_SLOTS];
+#pragma unroll
+    for (int m = 0; m < STAGE_SLOTS; ++m) {
+      half[m] = src[m].kind == 2 && sizeof(T) == 2;
+      from[m] = src[m].kind == 0 ? reinterpret_cast<const char*>(a.decay) : src[m].p;
+      if (src[m].kind == 0) src[m].stride = 0;
+    }
+    uint32_t regs[STAGE_SLOTS][CHUNK];
+    auto fetch_chunk = [&](int c0) {
+#pragma unroll
+      for (int tt = 0; tt < CHUNK; ++tt) {
+        const int64_t t = t0 + (c0 + tt < n ? c0 + tt : n - 1);
+#pragma unroll
+        for (int m = 0; m < STAGE_SLOTS; ++m) {
+          const char* at_t = from[m] + t * src[m].stride;
+          regs[m][tt] = half[m] ? (uint32_t)*reinterpret_cast<const unsigned short*>(at_t)
+                                : *reinterpret_cast<const uint32_t*>(at_t);
+        }
+      }
+    };
+    auto store_chunk = [&](float* buf) {
+#pragma unroll
+      for (int m = 0; m < STAGE_SLOTS; ++m) {
+        if (at[m] < 0) continue;
+#pragma unroll
+        for (int tt = 0; tt < CHUNK; ++tt) {
+          float v = half[m] ? __uint_as_float(regs[m][tt] << 16) : __uint_as_float(regs[m][tt]);
+          if (src[m].kind == 0) v = 0.f;
+          buf[tt * stride + at[m]] = v;
+        }
+      }
+    };
+    fetch_chunk(0);
+    store_chunk(smem);
+    __syncthreads();
+    int turn = 0;
+    for (int c0 = 0; c0 < n; c0 += CHUNK, turn ^= 1) {
+      const bool more = c0 + CHUNK < n;
+      if (more) fetch_chunk(c0 + CHUNK);
+      walk(smem + turn * CHUNK * stride, c0, n - c0 < CHUNK ? n - c0 : CHUNK);
+      if (more) store_chunk(smem + (turn ^ 1) * CHUNK * stride);
+      __syncthreads();
+    }
+  } else {
+    for (int c0 = 0; c0 < n; c0 += CHUNK) {
+      const int cn = n - c0 < CHUNK ? n - c0 : CHUNK;
+      __syncthreads();
+      for (int e = tid; e < cn * per_token; e += blockDim.x) {
+        const int tt = e / per_token, k = e - tt * per_token;
+        smem[tt * stride + place(k)] = fetch(source(k), t0 + c0 + tt);
+      }
+      __syncthreads();
+      walk(smem, c0, cn);
     }
   }
   if (active) {
@@ -362,7 +470,8 @@ __global__ void __launch_bounds__(128) rule_kernel(RuleArgs a) {
 // read-out: per-head RMSNorm, a gain, a gate
 // ---------------------------------------------------------------------------------------
 // out[t, h, j] = o[t, h, j] * rsqrt(mean_j o^2 + eps) * gain[shared ? j : h dv + j] * gate
-//   gate_mode 0: gate_f32[t, h dv + j] as it is; 1: silu(gate_x[t, h dv + j]) from the engine's type
+//   gate_mode 0: gate_f32[t, h dv + j] as it is; 1: silu(gate_x[t, h dv + j]) from the engine's type;
+//   2: sigmoid(gate_f32[t, h dv + j])
 template <typename T>
 __global__ void __launch_bounds__(PREP_THREADS) head_rms_gate_kernel(const float* __restrict__ o, const float* __restrict__ gain,
                                                                      const float* __restrict__ gate_f32,
@@ -380,7 +489,8 @@ __global__ void __launch_bounds__(PREP_THREADS) head_rms_gate_kernel(const float
     ss = ls_warp_sum(ss);
     const float rstd = 1.0f / sqrtf(ss / (float)dv + eps);
     for (int j = lane; j < dv; j += 32) {
-      const float gt = gate_mode == 0 ? gate_f32[base + j] : silu_f(ls_to_float<T>(gate_x[base + j]));
+      const float gt = gate_mode == 0 ? gate_f32[base + j]
+                       : gate_mode == 2 ? sigmoid_f(gate_f32[base + j]) : silu_f(ls_to_float<T>(gate_x[base + j]));
       out[base + j] = ls_from_float<T>(o[base + j] * rstd * gain[gain_shared ? j : h * dv + j] * gt);
     }
   }
@@ -402,19 +512,17 @@ LS_API int ls_find_portions(const int* token_slot, int tokens, int* out, int cap
   return ls_launch_status();
 }
 
-LS_API int ls_delta_prep(const void* proj, int64_t ld, int dtype, const float* conv_w, const void* w_a2,
-                         const float* dt_bias, const float* a_log, const void* w_g2, const float* state,
-                         int64_t state_stride, const int* token_slot, float* qkv, float* decay, float* beta,
-                         float* gate, int tokens, int H, int G, int dk, int dv, int taps, int Ra, int Rg,
+LS_API int ls_delta_prep(const void* proj, int64_t ld, int dtype, const float* conv_w, const float* dt_bias,
+                         const float* a_log, const float* state, int64_t state_stride, const int* token_slot,
+                         float* qkv, float* decay, float* beta, int tokens, int H, int G, int dk, int dv, int taps,
                          float unit_eps, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (H <= 0 || G <= 0 || H % G || dk <= 0 || dv <= 0 || taps < 1 || taps > MAX_TAPS || Ra <= 0 || Rg <= 0) return LS_E_SIZE;
+  if (H <= 0 || G <= 0 || H % G || dk <= 0 || dv <= 0 || taps < 1 || taps > MAX_TAPS) return LS_E_SIZE;
   DeltaPrepArgs a;
-  a.proj = proj; a.ld = ld; a.conv_w = conv_w; a.w_a2 = w_a2; a.dt_bias = dt_bias; a.a_log = a_log; a.w_g2 = w_g2;
-  a.state = state; a.state_stride = state_stride; a.token_slot = token_slot; a.qkv = qkv; a.decay = decay;
-  a.beta = beta; a.gate = gate; a.T = tokens; a.H = H; a.G = G; a.dk = dk; a.dv = dv; a.taps = taps; a.Ra = Ra;
-  a.Rg = Rg; a.unit_eps = unit_eps;
-  const size_t smem = sizeof(float) * (size_t)(2 * G * dk + H * dv + Ra + Rg + 2 * G);
+  a.proj = proj; a.ld = ld; a.conv_w = conv_w; a.dt_bias = dt_bias; a.a_log = a_log; a.state = state;
+  a.state_stride = state_stride; a.token_slot = token_slot; a.qkv = qkv; a.decay = decay; a.beta = beta; a.T = tokens;
+  a.H = H; a.G = G; a.dk = dk; a.dv = dv; a.taps = taps; a.unit_eps = unit_eps;
+  const size_t smem = sizeof(float) * (size_t)(2 * G * dk + H * dv + 2 * G);
   if (smem > 200 * 1024) return LS_E_SMEM;
   LS_COUNT(LS_K_DELTA_PREP);
   cudaError_t e;
@@ -425,6 +533,16 @@ LS_API int ls_delta_prep(const void* proj, int64_t ld, int dtype, const float* c
     if (smem > 48 * 1024) cudaFuncSetAttribute(delta_prep_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     e = ls_launch(delta_prep_kernel<__nv_bfloat16>, dim3(tokens), dim3(PREP_THREADS), smem, stream, a);
   } else return LS_E_DTYPE;
+  if (e != cudaSuccess) return (int)e;
+  return ls_launch_status();
+}
+
+LS_API int ls_double_exp_decay(float* z, const float* bias, long long count, int channels, cudaStream_t stream) {
+  if (count <= 0) return 0;
+  if (channels <= 0) return LS_E_SIZE;
+  LS_COUNT(LS_K_DOUBLE_EXP_DECAY);
+  const dim3 grid((unsigned)((count + PREP_THREADS - 1) / PREP_THREADS));
+  cudaError_t e = ls_launch(double_exp_decay_kernel, grid, dim3(PREP_THREADS), 0, stream, z, bias, (int64_t)count, channels);
   if (e != cudaSuccess) return (int)e;
   return ls_launch_status();
 }
@@ -447,19 +565,13 @@ LS_API int ls_shift_mix(const void* x, int dtype, const float* mu, const float* 
   return ls_launch_status();
 }
 
-LS_API int ls_lowrank_decay(const void* low, const void* w2, int dtype, const float* w0, float* decay, int tokens,
-                            int channels, int rank, cudaStream_t stream) {
-  if (tokens <= 0) return 0;
-  if (channels <= 0 || rank <= 0 || rank > 8192) return LS_E_SIZE;
-  LS_COUNT(LS_K_LOWRANK_DECAY);
-  const size_t smem = sizeof(float) * (size_t)rank;
+LS_API int ls_tanh_rows(void* x, int dtype, long long count, cudaStream_t stream) {
+  if (count <= 0) return 0;
+  LS_COUNT(LS_K_TANH);
+  const dim3 grid((unsigned)((count + PREP_THREADS - 1) / PREP_THREADS));
   cudaError_t e;
-  if (dtype == LS_F32)
-    e = ls_launch(lowrank_decay_kernel<float>, dim3(tokens), dim3(PREP_THREADS), smem, stream, (const float*)low,
-                  (const float*)w2, w0, decay, channels, rank);
-  else if (dtype == LS_BF16)
-    e = ls_launch(lowrank_decay_kernel<__nv_bfloat16>, dim3(tokens), dim3(PREP_THREADS), smem, stream,
-                  (const __nv_bfloat16*)low, (const __nv_bfloat16*)w2, w0, decay, channels, rank);
+  if (dtype == LS_F32) e = ls_launch(tanh_kernel<float>, grid, dim3(PREP_THREADS), 0, stream, (float*)x, (int64_t)count);
+  else if (dtype == LS_BF16) e = ls_launch(tanh_kernel<__nv_bfloat16>, grid, dim3(PREP_THREADS), 0, stream, (__nv_bfloat16*)x, (int64_t)count);
   else return LS_E_DTYPE;
   if (e != cudaSuccess) return (int)e;
   return ls_launch_status();
@@ -468,11 +580,11 @@ LS_API int ls_lowrank_decay(const void* low, const void* w2, int dtype, const fl
 // rule 0: the gated delta rule; rule 1: the wkv rule.  `dtype`: the engine's type (of r, k, v for
 // rule 1, and of carry_src for both).
 LS_API int ls_state_rule(int rule, int dtype, const int* portions, int max_portions, float* state, int64_t state_stride,
-                         const void* in_a, const void* in_b, const void* in_v, const float* decay, const float* beta,
-                         const float* bonus, float* out, const void* carry_src, int64_t carry_ld, int carry_width,
+                         const void* in_a, const void* in_b, const void* in_v, const float* decay,
+                         const float* beta, const float* bonus, float* out, const void* carry_src, int64_t carry_ld, int carry_width,
                          int carry_rows, int H, int G, int dk, int dv, cudaStream_t stream) {
   if (max_portions <= 0) return 0;
-  if (H <= 0 || G <= 0 || H % G || dk <= 0 || dk > 8 * ROWS || dv <= 0 || carry_rows < 0 || carry_rows >= MAX_TAPS) return LS_E_SIZE;
+  if (H <= 0 || G <= 0 || H % G || dk <= 0 || dk > 16 * ROWS || dv <= 0 || carry_rows < 0 || carry_rows >= MAX_TAPS) return LS_E_SIZE;
   if (H > 65535) return LS_E_SIZE;
   RuleArgs a;
   a.portions = portions; a.state = state; a.state_stride = state_stride; a.in_a = in_a; a.in_b = in_b; a.in_v = in_v;
@@ -484,7 +596,19 @@ LS_API int ls_state_rule(int rule, int dtype, const int* portions, int max_porti
   while (threads > 32 && (threads / 2) / a.lanes >= dv) threads /= 2;
   const int cb = threads / a.lanes;
   const dim3 grid(max_portions, H, (dv + cb - 1) / cb);
-  const size_t smem = sizeof(float) * (size_t)CHUNK * (3 * dk + cb + 1);
+  // two buffers of CHUNK tokens, a token as the kernel lays it out
+  const size_t smem = sizeof(float) * 2 * (size_t)CHUNK * (3 * a.lanes * (ROWS + 4) + ((cb + 3) & ~3) + 4);
+  static bool configured = false;
+  if (!configured) {
+    const int most = 96 * 1024;
+    if (cudaFuncSetAttribute(rule_kernel<RULE_DELTA, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) != cudaSuccess ||
+        cudaFuncSetAttribute(rule_kernel<RULE_DELTA, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) != cudaSuccess ||
+        cudaFuncSetAttribute(rule_kernel<RULE_WKV, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) != cudaSuccess ||
+        cudaFuncSetAttribute(rule_kernel<RULE_WKV, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) != cudaSuccess)
+      return LS_E_SMEM;
+    configured = true;
+  }
+  if (smem > 96 * 1024) return LS_E_SMEM;
   cudaError_t e;
   if (rule == RULE_DELTA) {
     LS_COUNT(LS_K_DELTA_RULE);
@@ -501,11 +625,13 @@ LS_API int ls_state_rule(int rule, int dtype, const int* portions, int max_porti
   return ls_launch_status();
 }
 
+// gate_logit: gate_f32 holds logits, the gate is their sigmoid
 LS_API int ls_head_rms_gate(const float* o, const float* gain, const float* gate_f32, const void* gate_x, void* out,
-                            int dtype, int tokens, int H, int dv, int gain_shared, float eps, cudaStream_t stream) {
+                            int dtype, int tokens, int H, int dv, int gain_shared, int gate_logit, float eps,
+                            cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (H <= 0 || dv <= 0 || (gate_f32 == nullptr) == (gate_x == nullptr)) return LS_E_SIZE;
-  const int mode = gate_f32 != nullptr ? 0 : 1;
+  const int mode = gate_f32 != nullptr ? (gate_logit ? 2 : 0) : 1;
   LS_COUNT(LS_K_HEAD_RMS_GATE);
   cudaError_t e;
   if (dtype == LS_F32)

@@ -92,17 +92,17 @@ _SIGNATURES["seq"] = {
                       c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                       c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p],
     "ls_find_portions": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p],
-    "ls_delta_prep": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
-                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                      c_int, c_int, c_float, c_void_p],
+    "ls_delta_prep": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
+                      c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+    "ls_double_exp_decay": [c_void_p, c_void_p, ctypes.c_longlong, c_int, c_void_p],
     "ls_shift_mix": [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int, c_int, c_int,
                      c_void_p],
-    "ls_lowrank_decay": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "ls_state_rule": [c_int, c_int, c_void_p, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
                       c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int,
                       c_void_p],
-    "ls_head_rms_gate": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+    "ls_head_rms_gate": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                          c_float, c_void_p],
+    "ls_tanh_rows": [c_void_p, c_int, ctypes.c_longlong, c_void_p],
     "ls_experts_tile_rows": [],
     "ls_experts_route": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
     "ls_experts_plan": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
@@ -316,15 +316,27 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
                                  _stream()), "silu_mul")
 
 
+def _rows(t: torch.Tensor, name: str) -> tuple[int, int]:
+    """(pointer, row pitch in elements) of a 2-D operand whose rows are contiguous: a whole
+    tensor, or a view of some columns of one."""
+    if not t.is_cuda:
+        raise KernelError(f"{name} must live on a CUDA device; there is no CPU fallback")
+    if t.dim() != 2 or t.stride(1) != 1 or (t.shape[0] > 1 and t.stride(0) < t.shape[1]):
+        raise KernelError(f"{name} must be two-dimensional with contiguous rows")
+    return t.data_ptr(), (t.stride(0) if t.shape[0] > 1 else t.shape[1])
+
+
 def gemm_nt_simt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPILOGUE_STORE) -> None:
-    """c = a @ w.T on the CUDA cores with the chosen epilogue (see csrc/gemm_simt.cu)."""
+    """c = a @ w.T on the CUDA cores with the chosen epilogue (see csrc/gemm_simt.cu).  ``a`` may
+    be a view of some columns of a wider tensor."""
     m, k = a.shape
     n = c.shape[1]
     rows_w = 2 * n if epilogue == EPILOGUE_SILU_MUL else n
     if w.shape != (rows_w, k) or c.shape[0] != m or a.dtype != w.dtype:
         raise KernelError(f"gemm_nt: shapes do not agree: a {tuple(a.shape)} w {tuple(w.shape)} c {tuple(c.shape)}")
+    ap, lda = _rows(a, "a")
     _check(library().ls_gemm_nt_simt(
-        _dev(a, "a"), _dev(w, "w"), _dev(c, "c"), _code(a), _code(c), m, n, k, k, k, n, epilogue,
+        ap, _dev(w, "w"), _dev(c, "c"), _code(a), _code(c), m, n, k, lda, k, n, epilogue,
         _stream()), "gemm_nt_simt")
 
 
@@ -446,8 +458,9 @@ def gemm_nt_tc(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int,
     rows_w = 2 * n if epilogue == EPILOGUE_SILU_MUL else n
     if w.shape != (rows_w, k) or c.shape[0] != m or a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError(f"gemm_nt_tc: shapes or types do not agree: a {tuple(a.shape)} w {tuple(w.shape)} c {tuple(c.shape)}")
+    ap, lda = _rows(a, "a")
     status = library("tc").ls_gemm_nt_tc(
-        _dev(a, "a"), _dev(w, "w"), _dev(c, "c"), _code(c), m, n, k, k, k, n, epilogue,
+        ap, _dev(w, "w"), _dev(c, "c"), _code(c), m, n, k, lda, k, n, epilogue,
         _dev(err, "err", torch.int32), _stream())
     if status in (-2, -3):
         return False
@@ -605,18 +618,26 @@ def find_portions(token_slot, out, cap: int, err) -> None:
                                            _stream()), "find_portions")
 
 
-def delta_prep(proj, conv_w, w_a2, dt_bias, a_log, w_g2, state, token_slot, qkv, decay, beta, gate, heads: int,
-               groups: int, dk: int, dv: int, taps: int, unit_eps: float) -> None:
+def delta_prep(proj, conv_w, dt_bias, a_log, state, token_slot, qkv, decay, beta, heads: int, groups: int, dk: int,
+               dv: int, taps: int, unit_eps: float) -> None:
     """What lies between the projections and the gated delta rule, a token a block: causal
-    convolution (carried inputs from ``state``) and silu of q, k, v, unit q and k, beta, the decay
-    per key channel and the output gate through their low-rank maps; float32 out."""
+    convolution (carried inputs from ``state``) and silu of q, k, v, unit q and k (q scaled),
+    beta = sigmoid of its column, and the decay per key channel, made in place from the output
+    of its low-rank map: ``decay`` <- exp(-exp(a_log[head]) softplus(decay + dt_bias)).  float32 out.
+    ``proj`` [tokens, >= 2 G dk + H dv + H]."""
     f32 = torch.float32
     _check(library("seq").ls_delta_prep(
-        _dev(proj, "proj"), proj.shape[1], _code(proj), _dev(conv_w, "conv_w", f32), _dev(w_a2, "w_a2", proj.dtype),
-        _dev(dt_bias, "dt_bias", f32), _dev(a_log, "a_log", f32), _dev(w_g2, "w_g2", proj.dtype),
-        _dev(state, "state", f32), state.shape[1], _dev(token_slot, "token_slot", torch.int32), _dev(qkv, "qkv", f32),
-        _dev(decay, "decay", f32), _dev(beta, "beta", f32), _dev(gate, "gate", f32), proj.shape[0], heads, groups,
-        dk, dv, taps, w_a2.shape[1], w_g2.shape[1], float(unit_eps), _stream()), "delta_prep")
+        _dev(proj, "proj"), proj.shape[1], _code(proj), _dev(conv_w, "conv_w", f32), _dev(dt_bias, "dt_bias", f32),
+        _dev(a_log, "a_log", f32), _dev(state, "state", f32), state.shape[1],
+        _dev(token_slot, "token_slot", torch.int32), _dev(qkv, "qkv", f32), _dev(decay, "decay", f32),
+        _dev(beta, "beta", f32), proj.shape[0], heads, groups, dk, dv, taps, float(unit_eps), _stream()), "delta_prep")
+
+
+def double_exp_decay(z, bias) -> None:
+    """z <- exp(-exp(z + bias)) in place (float32 [tokens, channels]): a decay from the output of
+    its low-rank map."""
+    _check(library("seq").ls_double_exp_decay(_dev(z, "z", torch.float32), _dev(bias, "bias", torch.float32),
+                                              z.numel(), z.shape[1], _stream()), "double_exp_decay")
 
 
 def shift_mix(x, mu, state, prev_offset: int, token_slot, out) -> None:
@@ -631,14 +652,9 @@ def shift_mix(x, mu, state, prev_offset: int, token_slot, out) -> None:
         _stream()), "shift_mix")
 
 
-def lowrank_decay(low, w2, w0, decay) -> None:
-    """decay[t, i] = exp(-exp(w2[i] . tanh(low[t]) + w0[i])), float32."""
-    tokens, rank = low.shape
-    if w2.shape[1] != rank or decay.shape != (tokens, w2.shape[0]) or w2.dtype != low.dtype:
-        raise KernelError("lowrank_decay: shapes do not agree")
-    _check(library("seq").ls_lowrank_decay(_dev(low, "low"), _dev(w2, "w2"), _code(low), _dev(w0, "w0", torch.float32),
-                                           _dev(decay, "decay", torch.float32), tokens, w2.shape[0], rank, _stream()),
-           "lowrank_decay")
+def tanh_rows(x) -> None:
+    """x <- tanh(x) in place."""
+    _check(library("seq").ls_tanh_rows(_dev(x, "x"), _code(x), x.numel(), _stream()), "tanh_rows")
 
 
 def state_rule(rule: int, dtype, portions, max_portions: int, state, in_a, in_b, in_v, decay, beta, bonus, out,
@@ -653,13 +669,14 @@ def state_rule(rule: int, dtype, portions, max_portions: int, state, in_a, in_b,
         carry_rows, heads, groups, dk, dv, _stream()), "state_rule")
 
 
-def head_rms_gate(o, gain, gate_f32, gate_x, out, heads: int, dv: int, gain_shared: bool, eps: float) -> None:
-    """out = o / rms_per_head(o) * gain * gate, where the gate is ``gate_f32`` as it is or
-    silu(``gate_x``)."""
+def head_rms_gate(o, gain, gate_f32, gate_x, out, heads: int, dv: int, gain_shared: bool, eps: float,
+                  gate_logit: bool = False) -> None:
+    """out = o / rms_per_head(o) * gain * gate, where the gate is ``gate_f32`` as it is (or its
+    sigmoid, ``gate_logit``), or silu(``gate_x``)."""
     _check(library("seq").ls_head_rms_gate(
         _dev(o, "o", torch.float32), _dev(gain, "gain", torch.float32), _opt(gate_f32, "gate_f32", torch.float32),
         _opt(gate_x, "gate_x", out.dtype), _dev(out, "out"), _code(out), o.shape[0], heads, dv,
-        1 if gain_shared else 0, float(eps), _stream()), "head_rms_gate")
+        1 if gain_shared else 0, 1 if gate_logit else 0, float(eps), _stream()), "head_rms_gate")
 
 
 def experts_tile_rows(tensor_cores: bool = False) -> int:

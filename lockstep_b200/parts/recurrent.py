@@ -27,6 +27,7 @@ import torch
 
 from .. import kernels as K
 from .base import CacheNeed, Mixer, Runtime, WeightSpec, register_part
+from .norm import NormedRows
 
 
 def portion_list(ctx, state: torch.Tensor, rt: Runtime):
@@ -48,6 +49,7 @@ def _f32(t: torch.Tensor) -> torch.Tensor:
 
 class GatedDelta(Mixer):
     graph_safe = True
+    accepts_normed_rows = True       # its one product of the mixer's input can make the norm itself
 
     def __init__(self, hidden_size, num_heads, num_kv_heads, key_dim, value_dim, conv_taps, norm_eps, unit_eps,
                  runtime: Runtime, decay_rank=None, gate_rank=None):
@@ -86,8 +88,15 @@ class GatedDelta(Mixer):
     def bind(self, t):
         if t["a1"].shape[0] != t["a2"].shape[1] or t["g1"].shape[0] != t["g2"].shape[1]:
             raise ValueError("the two halves of a low-rank map do not have the same rank")
-        # one product for everything that reads the mixer's input
-        self.w_in = torch.cat([t["q"], t["k"], t["v"], t["b"], t["a1"], t["g1"]], dim=0).contiguous()
+        # one product for everything that reads the mixer's input: q, k, v, beta, then (from a column
+        # that is a multiple of 8, so that the next products can take them where they lie) the
+        # inputs of the two low-rank maps
+        zeros = lambda rows: torch.zeros((rows, self.w), dtype=t["q"].dtype, device=t["q"].device)
+        self.low_at = -(-(self.C + self.H) // 8) * 8
+        parts = [t["q"], t["k"], t["v"], t["b"], zeros(self.low_at - self.C - self.H), t["a1"], t["g1"]]
+        self.ra, self.rg = t["a1"].shape[0], t["g1"].shape[0]
+        parts.append(zeros(-(self.low_at + self.ra + self.rg) % 8))
+        self.w_in = torch.cat(parts, dim=0).contiguous()
         self.conv_w = _f32(torch.cat([t["q.conv"], t["k.conv"], t["v.conv"]], dim=0))
         self.w_a2, self.w_g2, self.w_o = t["a2"].contiguous(), t["g2"].contiguous(), t["o"]
         self.dt_bias, self.a_log, self.gain = _f32(t["dt_bias"]), _f32(t["A_log"]), _f32(t["norm"])
@@ -96,19 +105,27 @@ class GatedDelta(Mixer):
         rt, tokens = self.rt, residual.shape[0]
         f32 = torch.float32
         proj = rt.rows(tokens, self.w_in.shape[0])
-        K.gemm_nt(x, self.w_in, proj, err=rt.err)
-        qkv = rt.rows(tokens, self.C, dtype=f32)
+        if isinstance(x, NormedRows):
+            x.linear(self.w_in, proj, K.EPILOGUE_STORE, rt.err)
+        else:
+            K.gemm_nt(x, self.w_in, proj, err=rt.err)
+        # the low-rank maps' second halves as products with float32 results: the decay's goes
+        # through the prep kernel (a token a block, beside the convolutions), the gate's to the
+        # read-out kernel, which takes its sigmoid
         decay = rt.rows(tokens, self.H * self.dk, dtype=f32)
+        z_gate = rt.rows(tokens, self.Vd, dtype=f32)
+        K.gemm_nt(proj[:, self.low_at:self.low_at + self.ra], self.w_a2, decay, err=rt.err)
+        K.gemm_nt(proj[:, self.low_at + self.ra:self.low_at + self.ra + self.rg], self.w_g2, z_gate, err=rt.err)
+        qkv = rt.rows(tokens, self.C, dtype=f32)
         beta = rt.rows(tokens, self.H, dtype=f32)
-        gate = rt.rows(tokens, self.Vd, dtype=f32)
-        K.delta_prep(proj, self.conv_w, self.w_a2, self.dt_bias, self.a_log, self.w_g2, cache.state, ctx.token_slot,
-                     qkv, decay, beta, gate, self.H, self.G, self.dk, self.dv, self.taps, self.unit_eps)
+        K.delta_prep(proj, self.conv_w, self.dt_bias, self.a_log, cache.state, ctx.token_slot, qkv, decay, beta,
+                     self.H, self.G, self.dk, self.dv, self.taps, self.unit_eps)
         portions, cap = portion_list(ctx, cache.state, rt)
         o = rt.rows(tokens, self.Vd, dtype=f32)
         K.state_rule(K.RULE_DELTA, rt.dtype, portions, cap, cache.state, qkv, None, None, decay, beta, None, o,
                      proj, self.C, self.taps - 1, self.H, self.G, self.dk, self.dv)
         y = rt.rows(tokens, self.Vd)
-        K.head_rms_gate(o, self.gain, gate, None, y, self.H, self.dv, True, self.eps)
+        K.head_rms_gate(o, self.gain, z_gate, None, y, self.H, self.dv, True, self.eps, gate_logit=True)
         K.gemm_nt(y, self.w_o, residual, K.EPILOGUE_RESIDUAL, err=rt.err)
 
 
@@ -157,8 +174,10 @@ class Wkv(Mixer):
         low = rt.rows(tokens, self.w_w1.shape[0])
         for i, (w, out) in enumerate(((self.w_r, r), (self.w_k, k), (self.w_v, v), (self.w_g, g), (self.w_w1, low))):
             K.gemm_nt(mixed[i], w, out, err=rt.err)
+        K.tanh_rows(low)
         decay = rt.rows(tokens, self.A, dtype=f32)
-        K.lowrank_decay(low, self.w_w2, self.w0, decay)
+        K.gemm_nt(low, self.w_w2, decay, err=rt.err)
+        K.double_exp_decay(decay, self.w0)
         portions, cap = portion_list(ctx, cache.state, rt)
         o = rt.rows(tokens, self.A, dtype=f32)
         K.state_rule(K.RULE_WKV, rt.dtype, portions, cap, cache.state, r, k, v, decay, None, self.bonus, o,
