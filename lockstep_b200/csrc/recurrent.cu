@@ -2,8 +2,8 @@
 //   - the gated delta rule with a decay per head and key channel,
 //   - an RWKV-style rule (decay per channel, a bonus for the current token),
 // and what stands around them: the list of a step's portions made on the device, short
-// causal convolutions with their carried inputs, the token shift, the low-rank maps to
-// decays and gates, and the gated per-head RMSNorm of the read-out.
+// causal convolutions with their carried inputs, the token shift, the decays from the outputs
+// of their low-rank maps (which run as products), and the gated per-head RMSNorm of the read-out.
 //
 // A step's token axis packs portions of several requests; a request appears once, so token t
 // continues the portion of token t - 1 exactly when both have the same slot.  Everything a
@@ -11,9 +11,10 @@
 // step replays with other portions in the same buffers.
 //
 // All state and everything that enters a recurrence is float32.  A token's arithmetic is the
-// same whatever portion it arrives in: states are walked token by token, dot products over
-// the key channels are a thread's ascending fused multiply-adds followed by an xor-tree over
-// the lanes that share a column.
+// same whatever portion it arrives in: states are walked token by token, a dot product over
+// the key channels is four interleaved chains of fused multiply-adds per thread (channel r of
+// the thread's run goes to chain r mod 4), added as (c0 + c1) + (c2 + c3), then an xor-tree
+// over the lanes that share a column.
 #include "common.cuh"
 
 namespace {
@@ -584,7 +585,7 @@ LS_API int ls_state_rule(int rule, int dtype, const int* portions, int max_porti
                          const float* beta, const float* bonus, float* out, const void* carry_src, int64_t carry_ld, int carry_width,
                          int carry_rows, int H, int G, int dk, int dv, cudaStream_t stream) {
   if (max_portions <= 0) return 0;
-  if (H <= 0 || G <= 0 || H % G || dk <= 0 || dk > 16 * ROWS || dv <= 0 || carry_rows < 0 || carry_rows >= MAX_TAPS) return LS_E_SIZE;
+  if (H <= 0 || G <= 0 || H % G || dk <= 0 || dk > 32 * ROWS || dv <= 0 || carry_rows < 0 || carry_rows >= MAX_TAPS) return LS_E_SIZE;
   if (H > 65535) return LS_E_SIZE;
   RuleArgs a;
   a.portions = portions; a.state = state; a.state_stride = state_stride; a.in_a = in_a; a.in_b = in_b; a.in_v = in_v;
