@@ -14,9 +14,9 @@ null for none).  Three mixers:
 - ``wkv``: token-shift mixes, a per-channel decay from a low-rank map, a bonus for the current
   token, a gated per-head RMSNorm of the read-out.
 
-The feed-forward is a mixture of experts: sigmoid scores, the ``top`` largest chosen, the score
-multiplies the expert's input, squared-ReLU experts without biases.  Norm gains are stored
-around zero (the gain is 1 + w).  The head is the embedding table.  Layer i's tensors start with
+The feed-forward is a mixture of experts: sigmoid scores, the ``top`` largest chosen, each chosen
+expert run on the token's row times its score, squared-ReLU experts without biases.  A norm's
+tensor w holds its gain minus one (the gain is 1 + w).  The head is the embedding table.  Layer i's tensors start with
 ``l<i>.``: ``norm1``, ``mix.*``, ``norm2``, ``mlp.*``.
 """
 

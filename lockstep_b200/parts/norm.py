@@ -1,6 +1,6 @@
 """RMSNorm: y = x * rsqrt(mean(x^2) + eps) * gain, all in float32
 (LockStep: engine/kernels/rmsnorm.py:30-38).  ``offset``: the stored tensor is the gain minus
-this number (a gain kept around zero: offset 1); the sum is made once, in float32, when the
+this number (a tensor that holds the gain minus one: offset 1); the sum is made once, in float32, when the
 weights arrive.  ``tensor``: the local name of the stored tensor ("weight"; "" where the norm's
 own prefix names it)."""
 

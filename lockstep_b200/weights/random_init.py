@@ -4,7 +4,7 @@ model.safetensors) from a configuration and a seed.
 Tensors are drawn in the order of their sorted names from one seeded CPU
 generator, so a (configuration, seed, dtype) names one model.  Matrices and
 tables are N(0, init_std), norm gains 1 + N(0, gain_std); a part may give a tensor a
-distribution of its own (``WeightSpec.init``: a gain stored around zero, a decay's bias).
+distribution of its own (``WeightSpec.init``: a norm's gain minus one, a decay's bias).
 """
 
 from __future__ import annotations

@@ -22,7 +22,7 @@ def rms(x, eps):
 
 
 def offset_norm(x, w, eps):
-    """The layer norm of the design: the gain is stored around zero."""
+    """The layer norm of the design: the tensor holds the gain minus one."""
     return rms(x, eps) * (1.0 + w)
 
 

@@ -143,7 +143,7 @@ def test_random_weights_use_the_parts_own_distributions(tmp_path):
     from safetensors.torch import load_file
 
     w = load_file(str(M.make_folder(tmp_path, M.MODEL_P, seed=4, dtype="float32") / "model.safetensors"))
-    assert abs(float(w["l0.norm1"].mean())) < 0.1                   # gains stored around zero
+    assert abs(float(w["l0.norm1"].mean())) < 0.1                   # the tensors hold gains minus one
     assert 0.0 <= float(w["l2.mix.mu.r"].min()) and float(w["l2.mix.mu.r"].max()) <= 1.0
     assert float(w["l2.mix.w0"].mean()) < -1.5
 
