@@ -69,7 +69,21 @@ MODEL_Q = model(96, 157, 3e-6, [
 ])
 PAGE_Q = 8
 
-MODELS = {"P": (MODEL_P, PAGE_P), "Q": (MODEL_Q, PAGE_Q)}
+# R: extremes.  A width that is no multiple of 8 (no row pitch of 16 bytes: the CUDA-core products also in
+# bfloat16), a single expert, all experts chosen, convolutions of one tap and of eight, eight query heads on
+# one key head at the size the tensor-core attention takes with values half as large, two readers of one
+# layer's keys (one without a window, so every key is kept), heads of 8
+MODEL_R = model(100, 300, 1e-6, [
+    with_mlp(wkv(5, 20, decay_rank=3), 36, 1, 1),
+    with_mlp(attention(8, 1, 128, 64, window=1000, rot=(128, 10000.0)), 36, 4, 4),
+    with_mlp(delta(2, 2, 64, 64, conv=1, decay_rank=8, gate_rank=8), 50, 9, 2),
+    with_mlp(attention(8, 1, 128, 64, window=17, rot=(128, 10000.0), kv_from=1), 36, 4, 4),
+    with_mlp(attention(8, 1, 128, 64, rot=(128, 10000.0), kv_from=1)),
+    with_mlp(delta(4, 1, 8, 8, conv=8), 36, 4, 1),
+])
+PAGE_R = 16
+
+MODELS = {"P": (MODEL_P, PAGE_P), "Q": (MODEL_Q, PAGE_Q), "R": (MODEL_R, PAGE_R)}
 
 
 def one_layer(layer, width=48, vocab=97, eps=1e-5):

@@ -242,12 +242,12 @@ def test_one_layer_models_in_every_cutting(zoo, name, dtype):
                 assert torch.equal(row, rows[plan_name][key]), (name, plan_name, key)
 
 
-LENGTHS = {"P": [70, 300, 37, 150, 129], "Q": [45, 210, 90, 33, 260]}
+LENGTHS = {"P": [70, 300, 37, 150, 129], "Q": [45, 210, 90, 33, 260], "R": [40, 190, 75, 131]}
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("plan_name", sorted(PLANS))
-@pytest.mark.parametrize("model", ["P", "Q"])
+@pytest.mark.parametrize("model", ["P", "Q", "R"])
 def test_whole_models_in_every_cutting(zoo, model, plan_name, dtype):
     config, page = M.MODELS[model]
     folder, requests, want = zoo(config, dtype, LENGTHS[model])
