@@ -113,6 +113,8 @@ __global__ void __launch_bounds__(PLAN_THREADS) plan_kernel(const int* __restric
 // One tile of an expert's product on the CUDA cores: C[rows, N] = A[rows, K] . W_e[N, K]^T.
 //   MODE 0 (up):   A row = x[row_token] * row_weight, C = relu(.)^2 in the engine's type
 //   MODE 1 (down): A row = act[row],                  C float32
+//   MODE 2 (down, one expert a token): C[row_token[row], :] += the product, float32: the sum into
+//   the residual stream, every element of which then has one writer
 template <typename T, int MODE>
 __global__ void __launch_bounds__(256) expert_product_kernel(const int* __restrict__ plan, const T* __restrict__ A,
                                                              const int* __restrict__ row_token,
@@ -179,8 +181,11 @@ __global__ void __launch_bounds__(256) expert_product_kernel(const int* __restri
       if (MODE == 0) {
         const float v = fmaxf(acc[i][j], 0.f);
         reinterpret_cast<T*>(Cout)[at] = ls_from_float<T>(v * v);
-      } else {
+      } else if (MODE == 1) {
         reinterpret_cast<float*>(Cout)[at] = acc[i][j];
+      } else {
+        float* to = reinterpret_cast<float*>(Cout) + (int64_t)row_token[row0 + r] * N + n;
+        *to = *to + acc[i][j];
       }
     }
   }
@@ -227,13 +232,15 @@ LS_API int ls_experts_plan(const int* ids, const float* weights, int tokens, int
   return ls_launch_status();
 }
 
-// mode 0: act[rows, N] = relu(x[row_token] * row_weight . W_e^T)^2; mode 1: y[rows, N] = act . W_e^T (float32).
+// mode 0: act[rows, N] = relu(x[row_token] * row_weight . W_e^T)^2; mode 1: y[rows, N] = act . W_e^T (float32);
+// mode 2: residual[row_token[row], :] += act . W_e^T (a token's one expert).
 // W [experts, N, K] in the engine's type.
 LS_API int ls_experts_product(int mode, int dtype, const int* plan, int max_tiles, const void* A, const int* row_token,
                               const float* row_weight, const void* W, void* C, int N, int K, cudaStream_t stream) {
   if (max_tiles <= 0) return 0;
   if (N <= 0 || K <= 0 || max_tiles > 65535) return LS_E_SIZE;     // (the plan's tiles hold up to TILE_M rows)
   const dim3 grid((N + TILE_N - 1) / TILE_N, max_tiles);
+  if (mode < 0 || mode > 2) return LS_E_SIZE;
   LS_COUNT(mode == 0 ? LS_K_EXPERTS_UP : LS_K_EXPERTS_DOWN);
   cudaError_t e;
   typedef __nv_bfloat16 bf16;
@@ -245,6 +252,10 @@ LS_API int ls_experts_product(int mode, int dtype, const int* plan, int max_tile
     e = ls_launch(expert_product_kernel<bf16, 0>, grid, dim3(256), 0, stream, plan, (const bf16*)A, row_token, row_weight, (const bf16*)W, C, N, K);
   else if (dtype == LS_BF16 && mode == 1)
     e = ls_launch(expert_product_kernel<bf16, 1>, grid, dim3(256), 0, stream, plan, (const bf16*)A, row_token, row_weight, (const bf16*)W, C, N, K);
+  else if (dtype == LS_F32 && mode == 2)
+    e = ls_launch(expert_product_kernel<float, 2>, grid, dim3(256), 0, stream, plan, (const float*)A, row_token, row_weight, (const float*)W, C, N, K);
+  else if (dtype == LS_BF16 && mode == 2)
+    e = ls_launch(expert_product_kernel<bf16, 2>, grid, dim3(256), 0, stream, plan, (const bf16*)A, row_token, row_weight, (const bf16*)W, C, N, K);
   else return LS_E_DTYPE;
   if (e != cudaSuccess) return (int)e;
   return ls_launch_status();

@@ -10,7 +10,9 @@
 // reads its neighbour's (or zeros past the end), and those lanes and columns are not stored.
 // An element is one accumulator over ascending K, so a row's result does not depend on the
 // tile it lies in.  Warps: TMA producer, MMA issuer (one elected lane), four epilogue warps.
-//   mode 0: C[row, n] = relu(acc)^2 as bfloat16;  mode 1: C[row, n] = acc as float32.
+//   mode 0: C[row, n] = relu(acc)^2 as bfloat16;  mode 1: C[row, n] = acc as float32;
+//   mode 2: C[row_token[row], n] += acc (float32): the sum into the residual stream where a token
+//   chooses one expert, so that every element has one writer.
 // ls_experts_gather writes the sorted, scaled rows that mode 0 reads.
 #include "tc_common.cuh"
 
@@ -28,8 +30,8 @@ constexpr uint32_t ACC_COLS = 128;
 template <int MODE>
 __global__ void __launch_bounds__(192) experts_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                                                          const __grid_constant__ CUtensorMap map_x,
-                                                         const int* __restrict__ plan, void* __restrict__ C, int N, int K,
-                                                         int* err) {
+                                                         const int* __restrict__ plan, const int* __restrict__ row_token,
+                                                         void* __restrict__ C, int N, int K, int* err) {
   ls_dependency_sync();
   const int tile = blockIdx.y;
   if (tile >= plan[0]) return;                    // the work list is sized for the worst case
@@ -142,8 +144,11 @@ __global__ void __launch_bounds__(192) experts_tc_kernel(const __grid_constant__
               if (MODE == 0) {
                 const float v = fmaxf(acc, 0.f);
                 reinterpret_cast<__nv_bfloat16*>(C)[at] = __float2bfloat16_rn(v * v);
-              } else {
+              } else if (MODE == 1) {
                 reinterpret_cast<float*>(C)[at] = acc;
+              } else {
+                float* to = reinterpret_cast<float*>(C) + (int64_t)row_token[row0 + c0 + j] * N + n;
+                *to = *to + acc;
               }
             }
           }
@@ -215,12 +220,15 @@ LS_API int ls_experts_gather(const void* x, const int* row_token, const float* r
 }
 
 // A [rows, K] bfloat16 sorted by expert as `plan` says (tiles of up to 128 rows), W [experts, N, K]
-// bfloat16; C [rows, N]: mode 0 bfloat16 relu(.)^2, mode 1 float32.  Returns LS_E_ALIGN or LS_E_SIZE,
-// having launched nothing, for what TMA cannot address; the caller then takes the CUDA-core product.
+// bfloat16; C [rows, N]: mode 0 bfloat16 relu(.)^2, mode 1 float32; mode 2: C [tokens, N] float32, added into
+// at row_token[row].  Returns LS_E_ALIGN or LS_E_SIZE, having launched nothing, for what TMA cannot
+// address; the caller then takes the CUDA-core product.
 LS_API int ls_experts_product_tc(int mode, const int* plan, int max_tiles, const void* A, long long rows, const void* W,
-                                 int experts, void* C, int N, int K, int* err, cudaStream_t stream) {
+                                 int experts, const int* row_token, void* C, int N, int K, int* err,
+                                 cudaStream_t stream) {
   if (max_tiles <= 0 || rows <= 0) return 0;
-  if (N <= 0 || K <= 0 || experts <= 0 || max_tiles > 65535 || (mode != 0 && mode != 1)) return LS_E_SIZE;
+  if (N <= 0 || K <= 0 || experts <= 0 || max_tiles > 65535 || mode < 0 || mode > 2) return LS_E_SIZE;
+  if (mode == 2 && row_token == nullptr) return LS_E_SIZE;
   if ((K % 8) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return LS_E_ALIGN;
   CUtensorMap mw, mx;
   if (!make_map(&mw, W, (long long)experts * N, K, BM)) return LS_E_SIZE;
@@ -228,14 +236,17 @@ LS_API int ls_experts_product_tc(int mode, const int* plan, int max_tiles, const
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(experts_tc_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM) != cudaSuccess ||
-        cudaFuncSetAttribute(experts_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM) != cudaSuccess)
+        cudaFuncSetAttribute(experts_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(experts_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM) != cudaSuccess)
       return LS_E_SMEM;
     configured = true;
   }
   const dim3 grid((N + BM - 1) / BM, max_tiles);
   LS_COUNT(mode == 0 ? LS_K_EXPERTS_UP_TC : LS_K_EXPERTS_DOWN_TC);
-  cudaError_t e = mode == 0 ? ls_launch(experts_tc_kernel<0>, grid, dim3(192), SMEM, stream, mw, mx, plan, C, N, K, err)
-                            : ls_launch(experts_tc_kernel<1>, grid, dim3(192), SMEM, stream, mw, mx, plan, C, N, K, err);
+  cudaError_t e =
+      mode == 0   ? ls_launch(experts_tc_kernel<0>, grid, dim3(192), SMEM, stream, mw, mx, plan, row_token, C, N, K, err)
+      : mode == 1 ? ls_launch(experts_tc_kernel<1>, grid, dim3(192), SMEM, stream, mw, mx, plan, row_token, C, N, K, err)
+                  : ls_launch(experts_tc_kernel<2>, grid, dim3(192), SMEM, stream, mw, mx, plan, row_token, C, N, K, err);
   if (e != cudaSuccess) return (int)e;
   return ls_launch_status();
 }

@@ -109,8 +109,8 @@ _SIGNATURES["seq"] = {
                         c_void_p, c_void_p],
     "ls_experts_tc_tile_rows": [],
     "ls_experts_gather": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
-    "ls_experts_product_tc": [c_int, c_void_p, c_int, c_void_p, ctypes.c_longlong, c_void_p, c_int, c_void_p, c_int,
-                              c_int, c_void_p, c_void_p],
+    "ls_experts_product_tc": [c_int, c_void_p, c_int, c_void_p, ctypes.c_longlong, c_void_p, c_int, c_void_p, c_void_p,
+                              c_int, c_int, c_void_p, c_void_p],
     "ls_experts_product": [c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                            c_int, c_void_p],
     "ls_experts_combine": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -705,7 +705,8 @@ def experts_plan(ids, weights, experts: int, tile_rows: int, plan, max_tiles: in
 
 def experts_product(mode: int, plan, max_tiles: int, a, row_token, row_weight, w, c) -> None:
     """mode 0: c[row] = relu((a[row_token[row]] * row_weight[row]) @ w[e].T)^2; mode 1: c[row] = a[row] @ w[e].T
-    in float32; rows sorted by expert as ``plan`` says.  w [experts, n, k]."""
+    in float32; mode 2: c[row_token[row]] += a[row] @ w[e].T (float32; for a token's one expert); rows sorted by
+    expert as ``plan`` says.  w [experts, n, k]."""
     n, k = w.shape[1], w.shape[2]
     if a.shape[1] != k or c.shape[1] != n or a.dtype != w.dtype:
         raise KernelError("experts_product: shapes do not agree")
@@ -733,18 +734,20 @@ def experts_gather(x, row_token, row_weight, out) -> None:
                                             width, _stream()), "experts_gather")
 
 
-def experts_product_tc(mode: int, plan, max_tiles: int, a, w, c, err) -> bool:
+def experts_product_tc(mode: int, plan, max_tiles: int, a, w, c, err, row_token=None) -> bool:
     """The experts' product on tcgen05 (csrc/experts_tc.cu): a [rows, k] bfloat16 sorted by expert, w
-    [experts, n, k] bfloat16; mode 0: c = relu(a @ w[e].T)^2 (bfloat16), mode 1: c = a @ w[e].T (float32).
+    [experts, n, k] bfloat16; mode 0: c = relu(a @ w[e].T)^2 (bfloat16), mode 1: c = a @ w[e].T (float32),
+    mode 2: c[row_token[row]] += a[row] @ w[e].T (float32 [tokens, n]; for a token's one expert).
     Returns False, having launched nothing, for what TMA cannot address."""
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not USE_TENSOR_CORES[0]:
         return False
     n, k = w.shape[1], w.shape[2]
-    if a.shape[1] != k or c.shape != (a.shape[0], n) or c.dtype != (torch.bfloat16 if mode == 0 else torch.float32):
+    if a.shape[1] != k or c.shape[1] != n or (mode != 2 and c.shape[0] != a.shape[0]) \
+            or c.dtype != (torch.bfloat16 if mode == 0 else torch.float32) or (mode == 2 and row_token is None):
         raise KernelError("experts_product_tc: shapes or types do not agree")
     status = library("seq").ls_experts_product_tc(
         mode, _dev(plan, "plan", torch.int32), max_tiles, _dev(a, "a"), a.shape[0], _dev(w, "w"), w.shape[0],
-        _dev(c, "c"), n, k, _dev(err, "err", torch.int32), _stream())
+        _opt(row_token, "row_token", torch.int32), _dev(c, "c"), n, k, _dev(err, "err", torch.int32), _stream())
     if status in (-2, -3):
         return False
     _check(status, "experts_product_tc")

@@ -64,17 +64,22 @@ class RoutedExperts(FeedForward):
         pair_row = rt.rows(pairs, dtype=i32)
         K.experts_plan(ids, weights, self.E, tile, plan, max_tiles, row_token, row_weight, pair_row, rt.err)
         act = rt.rows(pairs, self.f)
-        y = rt.rows(pairs, self.h, dtype=f32)
+        # one expert a token: the second product adds into the residual stream itself (an element has
+        # one writer); more: its rows go through memory and are added in order of rank
+        alone = self.top == 1
+        y = residual if alone else rt.rows(pairs, self.h, dtype=f32)
+        down = 2 if alone else 1
         if tensor_cores:
             scaled = rt.rows(pairs, self.h)
             K.experts_gather(x, row_token, row_weight, scaled)
             if not (K.experts_product_tc(0, plan, max_tiles, scaled, self.w_up, act, rt.err)
-                    and K.experts_product_tc(1, plan, max_tiles, act, self.w_down, y, rt.err)):
+                    and K.experts_product_tc(down, plan, max_tiles, act, self.w_down, y, rt.err, row_token)):
                 raise K.KernelError("routed_experts: the tensor-core product refused shapes it was chosen for")
         else:
             K.experts_product(0, plan, max_tiles, x, row_token, row_weight, self.w_up, act)
-            K.experts_product(1, plan, max_tiles, act, row_token, row_weight, self.w_down, y)
-        K.experts_combine(y, pair_row, residual, self.top)
+            K.experts_product(down, plan, max_tiles, act, row_token, row_weight, self.w_down, y)
+        if not alone:
+            K.experts_combine(y, pair_row, residual, self.top)
 
 
 @register_part("feed_forward", "routed_experts")
