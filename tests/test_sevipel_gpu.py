@@ -262,6 +262,29 @@ def test_whole_models_in_every_cutting(zoo, model, plan_name, dtype):
         assert runner.graphs.replays > 100               # decoded tokens ran as recorded steps
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_of_a_repeating_shape_are_recorded_and_replayed(zoo, dtype):
+    """Portions of 300 tokens with one wanted row: the shape comes again and again, so from its
+    third occurrence the step is a recorded one (the portion list, the experts' work lists and
+    the states' slots are all read on the device at replay)."""
+    config, page = M.MODELS["P"]
+    folder, requests, want = zoo(config, dtype, [900, 900, 601], key="recorded")
+    steps = []
+    for uid, toks in requests.items():
+        for i in range(0, len(toks) - 1, 300):
+            n = min(300, len(toks) - i)
+            steps.append({"entries": [(uid, toks[i:i + n], [n - 1, 0])], "end": [uid] if i + n == len(toks) else []})
+    steps.append({"entries": [("r2", requests["r2"][600:601], [0])], "end": ["r2"]})   # the last request ends on a single token
+    runner = make_runner(folder, dtype, page, steps, max_live=2)
+    rows = H.run_plan(runner, steps)
+    assert runner.graphs is not None and runner.graphs.mixed_replays >= 4
+    M.assert_close(rows, want, dtype, "recorded steps of 300 tokens")
+    fresh = make_runner(folder, dtype, page, steps, max_live=2, use_graphs=False)
+    plain_rows = H.run_plan(fresh, steps)
+    for key, row in rows.items():
+        assert torch.equal(row, plain_rows[key]), key      # a replayed step gives the bits of an unrecorded one
+
+
 def _sharpen(tensors):
     # a large gain on the keys' and queries' norm makes every row of the softmax pick one or two
     # keys: a key that is wrongly seen or not seen at a window's edge, or a far key that is lost,
