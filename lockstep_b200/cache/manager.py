@@ -33,6 +33,7 @@ class LayerCache:
     block_table: torch.Tensor | None = None   # [max_live, max_pages_per_seq] int32 (device)
     state: torch.Tensor | None = None         # [max_live, *state_shape]
     group: object | None = None
+    parts: tuple = ()                         # kind "several": one LayerCache per need, in the need's order
 
 
 @dataclass
@@ -250,12 +251,26 @@ class CacheManager:
         self.device = torch.device(device)
         self.paged: list[PagedGroup] = []
         self.states: list[StateGroup] = []
-        self._entry: dict[int, tuple[object, int]] = {}
-        by_key: dict[tuple, list[int]] = {}
+        self._entry: dict[object, tuple[object, int]] = {}
+        self._several: dict[int, list] = {}
+        by_key: dict[tuple, list] = {}
         need_of: dict[tuple, CacheNeed] = {}
+        # an entry whose need is "several" stands for one entry per part, named (entry, i)
+        flat: list[tuple[object, CacheNeed]] = []
         for entry, need in enumerate(needs):
             if need is None:
                 continue
+            if need.kind == "several":
+                self._several[entry] = []
+                for i, sub in enumerate(need.parts):
+                    if sub is not None and sub.kind == "several":
+                        raise ValueError("a cache need of several parts cannot hold another such need")
+                    self._several[entry].append(None if sub is None else (entry, i))
+                    if sub is not None:
+                        flat.append(((entry, i), sub))
+            else:
+                flat.append((entry, need))
+        for entry, need in flat:
             by_key.setdefault(need.group_key(), []).append(entry)
             need_of[need.group_key()] = need
         max_pages_per_seq = -(-self.max_seq_len // self.page_size)
@@ -376,7 +391,11 @@ class CacheManager:
         for g in self.paged:
             g.sync()
 
-    def view(self, entry: int, writes: bool = True) -> LayerCache:
+    def view(self, entry, writes: bool = True) -> LayerCache:
+        if entry in self._several:
+            return LayerCache(kind="several", writes=writes, parts=tuple(
+                LayerCache(kind="none", writes=False) if e is None else self.view(e, writes)
+                for e in self._several[entry]))
         if entry not in self._entry:
             return LayerCache(kind="none", writes=False)
         group, index = self._entry[entry]

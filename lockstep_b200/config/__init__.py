@@ -7,9 +7,11 @@ from . import qwen3 as _qwen3  # registers Qwen3ForCausalLM
 from .qwen3 import Qwen3Config
 from . import sevipel as _sevipel  # registers Sevipel
 from .sevipel import SevipelConfig
+from . import malazen as _malazen  # registers Malazen
+from .malazen import MalazenConfig
 
 __all__ = [
-    "ConfigError", "LayerRun", "LayerSpec", "ModelSpec", "PartSpec", "Qwen3Config", "SevipelConfig",
+    "ConfigError", "LayerRun", "LayerSpec", "MalazenConfig", "ModelSpec", "PartSpec", "Qwen3Config", "SevipelConfig",
     "architecture_name", "config_from_dict", "known_architectures", "load_config",
     "own_tensors", "register_architecture", "tensor_name", "unregister_architecture",
 ]

@@ -65,12 +65,15 @@ class LayerRun:
 
     A layer may be run more than once (give each run its own ``cache``), and a
     run may read a cache entry that an earlier run wrote (``writes_cache``
-    False): it then adds nothing to the cache.
+    False): it then adds nothing to the cache.  ``add_embedding``: the embedding's output for
+    the step's tokens is added to the residual stream right before this run (a model that
+    passes over some of its layers several times and feeds the embedding in again each time).
     """
 
     layer: int
     cache: int
     writes_cache: bool = True
+    add_embedding: bool = False
 
 
 @dataclass(frozen=True)

@@ -2,6 +2,7 @@
 // every kernel that folds, so that all of them produce the same bits.
 #pragma once
 
+#include <math.h>
 #include <math_constants.h>
 
 #include "common.cuh"
@@ -23,7 +24,8 @@ __device__ __forceinline__ float ls_fold_value(float run, float alpha, float par
 // together (independent loads) before they are folded one after the other.
 __device__ __forceinline__ float ls_fold_row(const float* __restrict__ part_acc,
                                              const float* __restrict__ part_ml, int64_t first,
-                                             int64_t stride, int n, int nq, int h, int d, int c) {
+                                             int64_t stride, int n, int nq, int h, int d, int c,
+                                             float sink = -INFINITY) {
   float acc = 0.f, m_run = -CUDART_INF_F, l_run = 0.f;
   for (int s0 = 0; s0 < n; s0 += 8) {
     float m_s[8], l_s[8], a_s[8];
@@ -48,6 +50,14 @@ __device__ __forceinline__ float ls_fold_row(const float* __restrict__ part_acc,
         }
       }
     }
+  }
+  // a sink (anything above -inf): one more term exp(sink) in the denominator, which has no value;
+  // folded in like a last partial whose weights sum to one and whose values are zero
+  if (sink != -CUDART_INF_F) {
+    float alpha, beta, m_new;
+    ls_fold_scales(m_run, sink, alpha, beta, m_new);
+    acc = __fmul_rn(acc, alpha);
+    l_run = ls_fold_value(l_run, alpha, 1.0f, beta);
   }
   return l_run > 0.f ? __fdiv_rn(acc, l_run) : 0.f;
 }

@@ -55,7 +55,8 @@ attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ pages, T* _
                       float* __restrict__ part_acc, float* __restrict__ part_ml,
                       const int* __restrict__ work, const int* __restrict__ block_table,
                       int table_stride, int nq, int nkv, int d, int page_size, int num_pages,
-                      int window, float scale, const float* __restrict__ slopes, int hb, int* err) {
+                      int window, float scale, const float* __restrict__ slopes,
+                      const float* __restrict__ log_rates, const float* __restrict__ sinks, int hb, int* err) {
   ls_dependency_sync();
   extern __shared__ __align__(16) float smem[];
   // rows of Q and K are d + 4 floats apart: 16-byte pieces stay aligned, and the eight key rows a
@@ -96,7 +97,10 @@ attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ pages, T* _
   const int h = h_first + m - m_tok * heads_at_once;           // this row's head
   // slopes (or null): a score gets slopes[head] x (key position - query position) added,
   // a position encoding that biases the scores instead of rotating queries and keys
+  // with log_rates as well the bias is logarithmic in the distance instead:
+  // - slopes[head] x ln(1 + log_rates[head] x (query position - key position))
   const float slope = slopes != nullptr && row_valid ? slopes[h] : 0.f;
+  const float log_rate = log_rates != nullptr && row_valid ? log_rates[h] : 0.f;
   __syncthreads();                                             // the heads before are done with Q
   for (int i = tid; i < TILE_M * d; i += 128) {
     const int r = i / d, c = i - r * d;
@@ -189,6 +193,7 @@ attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ pages, T* _
           const int key = n0 + sub + 8 * j;
           const bool keep = key < s_hi && key <= qpos && key >= row_lo;
           s[j] = !keep ? -CUDART_INF_F
+                 : log_rates != nullptr ? dot[j] * scale - slope * log1pf(log_rate * (float)(qpos - key))
                  : slopes != nullptr ? fmaf(slope, (float)(key - qpos), dot[j] * scale) : dot[j] * scale;
           tile_max = fmaxf(tile_max, s[j]);
         }
@@ -276,6 +281,16 @@ attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ pages, T* _
     }
   }
 
+  if (slot_base < 0 && row_valid && sinks != nullptr) {
+    // a sink: one more term exp(sinks[head]) in the softmax's denominator, with no value; folded in
+    // like a last split whose weights sum to one and whose values are zero
+    float alpha, beta, m_new;
+    ls_fold_scales(m_run, sinks[h], alpha, beta, m_new);
+#pragma unroll
+    for (int j = 0; j < MAX_D / 8; ++j) acc_run[j] = __fmul_rn(acc_run[j], alpha);
+    l_run = ls_fold_value(l_run, alpha, 1.0f, beta);
+    m_run = m_new;
+  }
   if (slot_base < 0 && row_valid) {
     T* o = out + ((int64_t)(tok0 + m_tok) * nq + h) * d;
 #pragma unroll
@@ -302,7 +317,8 @@ attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ pages,
                         float* __restrict__ part_acc, float* __restrict__ part_ml,
                         const int* __restrict__ work, const int* __restrict__ block_table,
                         int table_stride, int nq, int nkv, int d, int page_size, int num_pages,
-                        int window, float scale, const float* __restrict__ slopes, int slot_limit, int* err) {
+                        int window, float scale, const float* __restrict__ slopes,
+                        const float* __restrict__ log_rates, int slot_limit, int* err) {
   ls_dependency_sync();
   extern __shared__ __align__(16) unsigned char dsm[];
   constexpr int VEC = 16 / sizeof(T);        // elements per 16-byte chunk
@@ -382,6 +398,7 @@ attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ pages,
       }
       const bool keep = key < s_hi && key >= row_lo;
       Ss[u] = !keep ? -CUDART_INF_F
+              : log_rates != nullptr ? dot * scale - slopes[kvh * group + g] * log1pf(log_rates[kvh * group + g] * (float)(pos - key))
               : slopes != nullptr ? fmaf(slopes[kvh * group + g], (float)(key - pos), dot * scale) : dot * scale;
     }
     __syncthreads();
@@ -444,7 +461,7 @@ template <typename T>
 __global__ void attention_combine_kernel(const float* __restrict__ part_acc,
                                          const float* __restrict__ part_ml, T* __restrict__ out,
                                          const int* __restrict__ items, int nq, int d, int slot_limit,
-                                         int* err) {
+                                         const float* __restrict__ sinks, int* err) {
   ls_dependency_sync();
   const int* it = items + (int64_t)blockIdx.x * 4;
   const int tok = it[0], first = it[1], stride = it[2], n = it[3];
@@ -458,7 +475,7 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_acc,
   }
   const int h = blockIdx.y;
   for (int c = threadIdx.x; c < d; c += blockDim.x)
-    out[((int64_t)tok * nq + h) * d + c] = ls_from_float<T>(ls_fold_row(part_acc, part_ml, first, stride, n, nq, h, d, c));
+    out[((int64_t)tok * nq + h) * d + c] = ls_from_float<T>(ls_fold_row(part_acc, part_ml, first, stride, n, nq, h, d, c, sinks != nullptr ? sinks[h] : -CUDART_INF_F));
 }
 
 size_t tile_smem_bytes(int d) {
@@ -485,8 +502,10 @@ LS_API int ls_attention_tile(const void* q, const void* pages, void* out, float*
                              float* part_ml, int dtype, const int* work, int n_work,
                              const int* block_table, int table_stride, int nq, int nkv, int d,
                              int page_size, int num_pages, int window, float scale,
-                             const float* slopes, int* err, cudaStream_t stream) {
+                             const float* slopes, const float* log_rates, const float* sinks, int* err,
+                             cudaStream_t stream) {
   if (n_work <= 0) return 0;
+  if (log_rates != nullptr && slopes == nullptr) return LS_E_SIZE;
   if (!shape_ok(nq, nkv, d, page_size, LS_SPLIT)) return LS_E_SIZE;
   if (nq > 65535) return LS_E_SIZE;
   if ((uintptr_t)pages & 15) return LS_E_ALIGN;      // keys and values are read 16 bytes at a time
@@ -507,7 +526,7 @@ LS_API int ls_attention_tile(const void* q, const void* pages, void* out, float*
     if (smem > set_f32) set_f32 = smem;
     LS_COUNT(LS_K_ATTENTION_TILE), ls_launch(attention_tile_kernel<float>, grid, 128, smem, stream, 
         (const float*)q, (const float*)pages, (float*)out, part_acc, part_ml, work, block_table,
-        table_stride, nq, nkv, d, page_size, num_pages, window, scale, slopes, hb, err);
+        table_stride, nq, nkv, d, page_size, num_pages, window, scale, slopes, log_rates, sinks, hb, err);
   } else if (dtype == LS_BF16) {
     e = smem <= set_bf16 ? cudaSuccess
                          : cudaFuncSetAttribute(attention_tile_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -516,7 +535,7 @@ LS_API int ls_attention_tile(const void* q, const void* pages, void* out, float*
     LS_COUNT(LS_K_ATTENTION_TILE), ls_launch(attention_tile_kernel<__nv_bfloat16>, grid, 128, smem, stream, 
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, (__nv_bfloat16*)out, part_acc,
         part_ml, work, block_table, table_stride, nq, nkv, d, page_size, num_pages, window, scale,
-        slopes, hb, err);
+        slopes, log_rates, sinks, hb, err);
   } else {
     return LS_E_DTYPE;
   }
@@ -529,9 +548,10 @@ namespace {
 int launch_attention_decode(const void* q, const void* pages, float* part_acc, float* part_ml,
                             int dtype, const int* work, int n_work, const int* block_table,
                             int table_stride, int nq, int nkv, int d, int page_size,
-                            int num_pages, int window, float scale, const float* slopes, int slot_limit,
-                            int* err, cudaStream_t stream) {
+                            int num_pages, int window, float scale, const float* slopes,
+                            const float* log_rates, int slot_limit, int* err, cudaStream_t stream) {
   if (n_work <= 0) return 0;
+  if (log_rates != nullptr && slopes == nullptr) return LS_E_SIZE;
   if (!shape_ok(nq, nkv, d, page_size, DEC_TILE)) return LS_E_SIZE;
   const int group = nq / nkv;
   if (group * d > 128 * DEC_ACC || nkv > 65535) return LS_E_SIZE;
@@ -546,7 +566,7 @@ int launch_attention_decode(const void* q, const void* pages, float* part_acc, f
     if (smem > set_f32) set_f32 = smem;
     LS_COUNT(LS_K_ATTENTION_DECODE), ls_launch(attention_decode_kernel<float>, grid, 128, smem, stream, 
         (const float*)q, (const float*)pages, part_acc, part_ml, work, block_table, table_stride,
-        nq, nkv, d, page_size, num_pages, window, scale, slopes, slot_limit, err);
+        nq, nkv, d, page_size, num_pages, window, scale, slopes, log_rates, slot_limit, err);
   } else if (dtype == LS_BF16) {
     const size_t smem = decode_smem_bytes(d, group, 2);
     e = smem <= set_bf16 ? cudaSuccess
@@ -555,7 +575,7 @@ int launch_attention_decode(const void* q, const void* pages, float* part_acc, f
     if (smem > set_bf16) set_bf16 = smem;
     LS_COUNT(LS_K_ATTENTION_DECODE), ls_launch(attention_decode_kernel<__nv_bfloat16>, grid, 128, smem, stream, 
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, part_acc, part_ml, work,
-        block_table, table_stride, nq, nkv, d, page_size, num_pages, window, scale, slopes, slot_limit, err);
+        block_table, table_stride, nq, nkv, d, page_size, num_pages, window, scale, slopes, log_rates, slot_limit, err);
   } else {
     return LS_E_DTYPE;
   }
@@ -563,16 +583,16 @@ int launch_attention_decode(const void* q, const void* pages, float* part_acc, f
 }
 
 int launch_attention_combine(const float* part_acc, const float* part_ml, void* out, int dtype,
-                             const int* items, int n_items, int nq, int d, int slot_limit, int* err,
-                             cudaStream_t stream) {
+                             const int* items, int n_items, int nq, int d, int slot_limit,
+                             const float* sinks, int* err, cudaStream_t stream) {
   if (n_items <= 0) return 0;
   if (nq > 65535) return LS_E_SIZE;
   dim3 grid(n_items, nq);
   const int threads = d >= 128 ? 128 : (d >= 64 ? 64 : 32);
   if (dtype == LS_F32)
-    LS_COUNT(LS_K_ATTENTION_COMBINE), ls_launch(attention_combine_kernel<float>, grid, threads, 0, stream, part_acc, part_ml, (float*)out, items, nq, d, slot_limit, err);
+    LS_COUNT(LS_K_ATTENTION_COMBINE), ls_launch(attention_combine_kernel<float>, grid, threads, 0, stream, part_acc, part_ml, (float*)out, items, nq, d, slot_limit, sinks, err);
   else if (dtype == LS_BF16)
-    LS_COUNT(LS_K_ATTENTION_COMBINE), ls_launch(attention_combine_kernel<__nv_bfloat16>, grid, threads, 0, stream, part_acc, part_ml, (__nv_bfloat16*)out, items, nq, d, slot_limit, err);
+    LS_COUNT(LS_K_ATTENTION_COMBINE), ls_launch(attention_combine_kernel<__nv_bfloat16>, grid, threads, 0, stream, part_acc, part_ml, (__nv_bfloat16*)out, items, nq, d, slot_limit, sinks, err);
   else
     return LS_E_DTYPE;
   return ls_launch_status();
@@ -585,16 +605,16 @@ int launch_attention_combine(const float* part_acc, const float* part_ml, void* 
 LS_API int ls_attention_decode(const void* q, const void* pages, float* part_acc, float* part_ml,
                                int dtype, const int* work, int n_work, const int* block_table,
                                int table_stride, int nq, int nkv, int d, int page_size,
-                               int num_pages, int window, float scale, const float* slopes, int* err,
-                               cudaStream_t stream) {
+                               int num_pages, int window, float scale, const float* slopes,
+                               const float* log_rates, int* err, cudaStream_t stream) {
   return launch_attention_decode(q, pages, part_acc, part_ml, dtype, work, n_work, block_table, table_stride, nq,
-                                 nkv, d, page_size, num_pages, window, scale, slopes, 0, err, stream);
+                                 nkv, d, page_size, num_pages, window, scale, slopes, log_rates, 0, err, stream);
 }
 
 LS_API int ls_attention_combine(const float* part_acc, const float* part_ml, void* out, int dtype,
-                                const int* items, int n_items, int nq, int d,
+                                const int* items, int n_items, int nq, int d, const float* sinks,
                                 cudaStream_t stream) {
-  return launch_attention_combine(part_acc, part_ml, out, dtype, items, n_items, nq, d, 0, nullptr, stream);
+  return launch_attention_combine(part_acc, part_ml, out, dtype, items, n_items, nq, d, 0, sinks, nullptr, stream);
 }
 
 // --------------------------------------------------------------------------
@@ -651,9 +671,9 @@ LS_API int ls_attention_decode_noalloc(const void* q, const void* pages, void* o
   // in the error word (LS_DEV_ROW_RANGE) and skipped, it cannot write outside the array
   const int status = launch_attention_decode(q, pages, part_acc, part_ml, dtype, work, n_work,
                                              block_table, table_stride, nq, nkv, d, page_size,
-                                             num_pages, window, scale, nullptr, n_slots, err, stream);
+                                             num_pages, window, scale, nullptr, nullptr, n_slots, err, stream);
   if (status != 0) return status;
-  return launch_attention_combine(part_acc, part_ml, out, dtype, combine, n_combine, nq, d, n_slots, err, stream);
+  return launch_attention_combine(part_acc, part_ml, out, dtype, combine, n_combine, nq, d, n_slots, nullptr, err, stream);
 }
 
 LS_API const char* ls_constants_attention_simt() {

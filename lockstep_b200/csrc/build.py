@@ -35,7 +35,7 @@ LIBRARIES: dict[str, list[str]] = {
     "tc": ["gemm_tc.cu", "attention_decode_mma.cu", "attention_prefill_tc.cu"],
     # mixers with a carried state, routed experts, projections with heads of unequal sizes:
     # loaded when a model first builds a part that needs them
-    "seq": ["heads_wide.cu", "recurrent.cu", "experts.cu", "experts_tc.cu"],
+    "seq": ["heads_wide.cu", "recurrent.cu", "experts.cu", "experts_tc.cu", "latent.cu"],
 }
 
 _HEADERS = ["common.cuh", "tc_common.cuh", "no_alloc.h", "rope.cuh", "attention_fold.cuh"]

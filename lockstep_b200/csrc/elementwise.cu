@@ -11,28 +11,35 @@
 // --------------------------------------------------------------------------
 template <typename T>
 __global__ void embed_gather_kernel(const int* __restrict__ ids, const T* __restrict__ table,
-                                    float* __restrict__ out, int width, int vocab, int* err) {
+                                    float* __restrict__ out, int width, int vocab, int accumulate, int* err) {
   ls_dependency_sync();
   const int t = blockIdx.x;
   const int id = ids[t];
   float* dst = out + (int64_t)t * width;
   if (id < 0 || id >= vocab) {
     if (threadIdx.x == 0) ls_record_fault(err, LS_DEV_TOKEN_RANGE, t);
-    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = 0.f;
+    if (!accumulate)
+      for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = 0.f;
     return;
   }
   const T* src = table + (int64_t)id * width;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = ls_to_float<T>(src[i]);
+  if (accumulate) {
+    // the token's embedding is added to a residual stream that already holds something (a
+    // model that feeds the embedding in again before a later pass over some of its layers)
+    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] += ls_to_float<T>(src[i]);
+  } else {
+    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = ls_to_float<T>(src[i]);
+  }
 }
 
 LS_API int ls_embed_gather(const int* ids, const void* table, int table_dtype, float* out,
-                           int tokens, int width, int vocab, int* err, cudaStream_t stream) {
+                           int tokens, int width, int vocab, int accumulate, int* err, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   const int threads = width >= 1024 ? 256 : 128;
   if (table_dtype == LS_F32)
-    LS_COUNT(LS_K_EMBED_GATHER), ls_launch(embed_gather_kernel<float>, tokens, threads, 0, stream, ids, (const float*)table, out, width, vocab, err);
+    LS_COUNT(LS_K_EMBED_GATHER), ls_launch(embed_gather_kernel<float>, tokens, threads, 0, stream, ids, (const float*)table, out, width, vocab, accumulate, err);
   else if (table_dtype == LS_BF16)
-    LS_COUNT(LS_K_EMBED_GATHER), ls_launch(embed_gather_kernel<__nv_bfloat16>, tokens, threads, 0, stream, ids, (const __nv_bfloat16*)table, out, width, vocab, err);
+    LS_COUNT(LS_K_EMBED_GATHER), ls_launch(embed_gather_kernel<__nv_bfloat16>, tokens, threads, 0, stream, ids, (const __nv_bfloat16*)table, out, width, vocab, accumulate, err);
   else
     return LS_E_DTYPE;
   return ls_launch_status();
@@ -87,20 +94,24 @@ __device__ __forceinline__ void rmsnorm_out4(TO* y, const TG* gain, const float*
 template <typename TO, typename TG>
 __global__ void __launch_bounds__(128)
 rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ row_index,
-               const TG* __restrict__ gain, TO* __restrict__ y, int rows, int width, int src_rows,
-               float eps, int* err) {
+               const TG* __restrict__ gain_all, TO* __restrict__ y, int rows, int width, int src_rows,
+               float eps, int parts, int* err) {
   ls_dependency_sync();
   constexpr int KEEP = 64;                    // floats a lane keeps: 16 float4
   const int lane = threadIdx.x & 31;
-  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (r >= rows) return;
+  // a row of `parts` equal consecutive parts, each normalised by its own root mean square, is
+  // `parts` rows of `width` elements to this kernel (the gain runs over the whole row)
+  const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (unit >= rows * parts) return;
+  const int r = unit / parts, part = unit - r * parts;
   int src = row_index ? row_index[r] : r;
   if (src < 0 || src >= src_rows) {
     if (lane == 0) ls_record_fault(err, LS_DEV_ROW_RANGE, r);
     src = 0;
   }
-  const float* xr = x + (int64_t)src * width;
-  TO* yr = y + (int64_t)r * width;
+  const float* xr = x + ((int64_t)src * parts + part) * width;
+  TO* yr = y + ((int64_t)r * parts + part) * width;
+  const TG* gain = gain_all + (int64_t)part * width;
   const bool vec = (width & 3) == 0 && ((uintptr_t)xr & 15) == 0;
   // four outputs an access where the outputs and the gains allow it (this changes no sum)
   const bool vec_out = ((uintptr_t)y & (4 * sizeof(TO) - 1)) == 0 && ((uintptr_t)gain & (4 * sizeof(TG) - 1)) == 0;
@@ -144,15 +155,17 @@ rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ row_index,
 }
 
 LS_API int ls_rmsnorm(const float* x, const int* row_index, const void* gain, int gain_dtype,
-                      void* y, int y_dtype, int rows, int width, int src_rows, float eps,
-                      int* err, cudaStream_t stream) {
+                      void* y, int y_dtype, int rows, int row_width, int src_rows, float eps,
+                      int parts, int* err, cudaStream_t stream) {
   if (rows <= 0) return 0;
+  if (parts <= 0 || row_width % parts) return LS_E_SIZE;
+  const int width = row_width / parts;
   // few rows: one warp per block, so that the rows spread over the device
-  const int warps = rows >= 1024 ? 4 : 1;
-  const int blocks = (rows + warps - 1) / warps;
+  const int warps = (int64_t)rows * parts >= 1024 ? 4 : 1;
+  const int blocks = (rows * parts + warps - 1) / warps;
 #define LS_RMS(TO, TG)                                                                          \
   LS_COUNT(LS_K_RMSNORM), ls_launch(rmsnorm_kernel<TO, TG>, blocks, warps * 32, 0, stream, x, row_index, (const TG*)gain, (TO*)y, \
-                                                            rows, width, src_rows, eps, err)
+                                                            rows, width, src_rows, eps, parts, err)
   if (y_dtype == LS_F32 && gain_dtype == LS_F32) LS_RMS(float, float);
   else if (y_dtype == LS_F32 && gain_dtype == LS_BF16) LS_RMS(float, __nv_bfloat16);
   else if (y_dtype == LS_BF16 && gain_dtype == LS_F32) LS_RMS(__nv_bfloat16, float);
@@ -404,6 +417,120 @@ LS_API int ls_silu_mul(const void* gate_up, void* out, int dtype, int rows, int 
     LS_COUNT(LS_K_SILU_MUL), ls_launch(silu_mul_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, rows, width);
   else
     return LS_E_DTYPE;
+  return ls_launch_status();
+}
+
+
+// --------------------------------------------------------------------------
+// Gated feed-forward activation with clamps: from a product's float32 or engine-type output
+// [rows, 2 * width] (gate columns, then up columns) and optional biases [2 * width]:
+//   g = min(gate + b, limit), u = clamp(up + b, -limit, limit), out = g * sigmoid(alpha g) * (u + 1)
+// computed in float32.  `residual` (or null): the bias of the projection that follows is added to
+// the float32 residual stream [rows, res_width] by the same launch, so that the product that
+// comes next only has to add itself.
+// --------------------------------------------------------------------------
+template <typename TI, typename TO, typename TB>
+__global__ void clamped_glu_kernel(const TI* __restrict__ gate_up, const TB* __restrict__ bias, TO* __restrict__ out,
+                                   int64_t rows, int width, float limit, float alpha, float* __restrict__ residual,
+                                   const TB* __restrict__ res_bias, int res_width) {
+  ls_dependency_sync();
+  const int64_t n = rows * width;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const int64_t r = i / width;
+    const int c = (int)(i - r * width);
+    float g = ls_to_float<TI>(gate_up[r * 2 * width + c]);
+    float u = ls_to_float<TI>(gate_up[r * 2 * width + width + c]);
+    if (bias != nullptr) {
+      g += ls_to_float<TB>(bias[c]);
+      u += ls_to_float<TB>(bias[width + c]);
+    }
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    out[i] = ls_from_float<TO>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+  }
+  if (residual != nullptr) {
+    const int64_t m = rows * res_width;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < m; i += stride)
+      residual[i] += ls_to_float<TB>(res_bias[i % res_width]);
+  }
+}
+
+LS_API int ls_clamped_glu(const void* gate_up, int in_dtype, const void* bias, int bias_dtype, void* out, int out_dtype,
+                          int rows, int width, float limit, float alpha, float* residual, const void* res_bias,
+                          int res_width, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (width <= 0 || (residual != nullptr && (res_bias == nullptr || res_width <= 0))) return LS_E_SIZE;
+  const int64_t n = (int64_t)rows * (width > res_width ? width : res_width);
+  const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+  LS_COUNT(LS_K_CLAMPED_GLU);
+#define LS_GLU(TI, TO, TB)                                                                                        \
+  ls_launch(clamped_glu_kernel<TI, TO, TB>, blocks, 256, 0, stream, (const TI*)gate_up, (const TB*)bias, (TO*)out, \
+            (int64_t)rows, width, limit, alpha, residual, (const TB*)res_bias, res_width)
+  if (in_dtype == LS_F32 && out_dtype == LS_F32 && bias_dtype == LS_F32) LS_GLU(float, float, float);
+  else if (in_dtype == LS_F32 && out_dtype == LS_BF16 && bias_dtype == LS_BF16) LS_GLU(float, __nv_bfloat16, __nv_bfloat16);
+  else if (in_dtype == LS_F32 && out_dtype == LS_BF16 && bias_dtype == LS_F32) LS_GLU(float, __nv_bfloat16, float);
+  else if (in_dtype == LS_BF16 && out_dtype == LS_BF16 && bias_dtype == LS_BF16) LS_GLU(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
+  else if (in_dtype == LS_BF16 && out_dtype == LS_BF16 && bias_dtype == LS_F32) LS_GLU(__nv_bfloat16, __nv_bfloat16, float);
+  else return LS_E_DTYPE;
+#undef LS_GLU
+  return ls_launch_status();
+}
+
+// --------------------------------------------------------------------------
+// rows of a float32 tensor set to a bias vector (or to zero), or the bias added to them:
+// what a product that adds itself into its output starts from.
+//   mode 0: x[r, :] = bias (zero where bias is null); mode 1: x[r, :] += bias
+// --------------------------------------------------------------------------
+template <typename TB>
+__global__ void row_bias_kernel(float* __restrict__ x, const TB* __restrict__ bias, int64_t rows, int width, int mode) {
+  ls_dependency_sync();
+  const int64_t n = rows * width;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const float b = bias != nullptr ? ls_to_float<TB>(bias[i % width]) : 0.f;
+    x[i] = mode == 0 ? b : x[i] + b;
+  }
+}
+
+LS_API int ls_row_bias(float* x, const void* bias, int bias_dtype, int rows, int width, int mode, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (width <= 0 || (mode != 0 && mode != 1) || (mode == 1 && bias == nullptr)) return LS_E_SIZE;
+  const int64_t n = (int64_t)rows * width;
+  const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+  LS_COUNT(LS_K_ROW_BIAS);
+  if (bias_dtype == LS_F32) ls_launch(row_bias_kernel<float>, blocks, 256, 0, stream, x, (const float*)bias, (int64_t)rows, width, mode);
+  else if (bias_dtype == LS_BF16) ls_launch(row_bias_kernel<__nv_bfloat16>, blocks, 256, 0, stream, x, (const __nv_bfloat16*)bias, (int64_t)rows, width, mode);
+  else return LS_E_DTYPE;
+  return ls_launch_status();
+}
+
+// --------------------------------------------------------------------------
+// residual += sum_b scale[b] * branch[b]  (float32; branches [n, count] one after the other):
+// the results of mixers that run side by side on the same input, each with a weight of its own
+// --------------------------------------------------------------------------
+constexpr int MAX_BRANCHES = 4;
+struct LsBranchScales { float s[MAX_BRANCHES]; };
+__global__ void weighted_sum_kernel(float* __restrict__ residual, const float* __restrict__ branches, int64_t count,
+                                    int n, LsBranchScales scales) {
+  ls_dependency_sync();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (int64_t)gridDim.x * blockDim.x) {
+    float sum = 0.f;
+#pragma unroll
+    for (int b = 0; b < MAX_BRANCHES; ++b)
+      if (b < n) sum = fmaf(scales.s[b], branches[(int64_t)b * count + i], sum);
+    residual[i] += sum;
+  }
+}
+
+LS_API int ls_weighted_sum(float* residual, const float* branches, long long count, int n, const float* scales,
+                           cudaStream_t stream) {
+  if (count <= 0) return 0;
+  if (n <= 0 || n > MAX_BRANCHES) return LS_E_SIZE;
+  LsBranchScales s;
+  for (int b = 0; b < MAX_BRANCHES; ++b) s.s[b] = b < n ? scales[b] : 0.f;
+  const int blocks = (int)((count + 255) / 256 < 148 * 16 ? (count + 255) / 256 : 148 * 16);
+  LS_COUNT(LS_K_WEIGHTED_SUM);
+  ls_launch(weighted_sum_kernel, blocks, 256, 0, stream, residual, branches, (int64_t)count, n, s);
   return ls_launch_status();
 }
 

@@ -2,7 +2,9 @@
 //   - an RMSNorm over the whole query projection and one over the whole key projection
 //     (gains of those sizes), or one per head, or none;
 //   - key heads of size d and value heads of size dv that need not be equal;
-//   - a layer that projects queries only (it reads another layer's keys and values).
+//   - a layer that projects queries only (it reads another layer's keys and values);
+//   - biases of the three projections, added here (in float32) rather than in the product;
+//   - a query temperature: the query of position p times 1 + coef ln(floor((p + 1) / every) + 1).
 // Queries go to q_out [tokens, nq * D], keys and values into the cache pages
 // [num_pages, 2, nkv, page_size, D]; D >= max(d, dv) is the one head size the attention
 // kernels then work with, and the elements past d (dv) are written as zeros: a zero in a
@@ -33,6 +35,10 @@ struct WideArgs {
   int scope;                // 0 none, 1 per head, 2 whole projection
   int has_kv, write_cache;
   float eps;
+  const void* bias;         // null, or [ld]: the biases of q, k, v in the order of the projection's columns
+  int bias_bf16;
+  float temp_coef;          // query temperature (0: none)
+  int temp_every;
 };
 
 __device__ __forceinline__ float gain_at(const void* g, int bf16, int i) {
@@ -40,12 +46,19 @@ __device__ __forceinline__ float gain_at(const void* g, int bf16, int i) {
               : reinterpret_cast<const float*>(g)[i];
 }
 
+// element i of a projection's row (at column `col0` of the whole row), with its bias
+template <typename T>
+__device__ __forceinline__ float biased_at(const WideArgs& a, const T* src, int col0, int i) {
+  const float v = ls_to_float<T>(src[i]);
+  return a.bias != nullptr ? v + gain_at(a.bias, a.bias_bf16, col0 + i) : v;
+}
+
 // sum of squares of src[0 .. n) by the whole block, fixed order
 template <typename T>
-__device__ float block_sumsq(const T* src, int n, float* scratch) {
+__device__ float block_sumsq(const WideArgs& a, const T* src, int col0, int n, float* scratch) {
   float ss = 0.f;
   for (int i = threadIdx.x; i < n; i += THREADS) {
-    const float v = ls_to_float<T>(src[i]);
+    const float v = biased_at<T>(a, src, col0, i);
     ss = fmaf(v, v, ss);
   }
   return ls_block_sum(ss, scratch);
@@ -54,8 +67,8 @@ __device__ float block_sumsq(const T* src, int n, float* scratch) {
 // One projection (q or k) of one token: heads of size d at src, normed, rotated, written as
 // heads of size D at dst(head) (the padding as zeros).
 template <typename T, typename Dst>
-__device__ void finish_heads(const WideArgs& a, const T* src, int heads, const void* gain, float rstd_whole,
-                             const float* cs, const float* sn, float* head_rstd, Dst dst) {
+__device__ void finish_heads(const WideArgs& a, const T* src, int col0, int heads, const void* gain, float rstd_whole,
+                             const float* cs, const float* sn, float* head_rstd, float factor, Dst dst) {
   const int d = a.d, D = a.D, half = a.rot_dim >> 1;
   if (a.scope == 1 && gain != nullptr) {
     // per-head sums: a warp per head, lanes strided, xor-tree
@@ -63,7 +76,7 @@ __device__ void finish_heads(const WideArgs& a, const T* src, int heads, const v
     for (int h = warp; h < heads; h += THREADS / 32) {
       float ss = 0.f;
       for (int i = lane; i < d; i += 32) {
-        const float v = ls_to_float<T>(src[h * d + i]);
+        const float v = biased_at<T>(a, src, col0, h * d + i);
         ss = fmaf(v, v, ss);
       }
       ss = ls_warp_sum(ss);
@@ -76,7 +89,7 @@ __device__ void finish_heads(const WideArgs& a, const T* src, int heads, const v
     float out = 0.f;
     if (i < d) {
       auto normed = [&](int j) {
-        float v = ls_to_float<T>(src[h * d + j]);
+        float v = biased_at<T>(a, src, col0, h * d + j);
         if (gain != nullptr) {
           v = __fmul_rn(v, a.scope == 2 ? rstd_whole : head_rstd[h]);
           v = __fmul_rn(v, gain_at(gain, a.gain_bf16, a.scope == 2 ? h * d + j : j));
@@ -94,6 +107,7 @@ __device__ void finish_heads(const WideArgs& a, const T* src, int heads, const v
       } else {
         out = normed(i);
       }
+      if (factor != 1.0f) out = __fmul_rn(out, factor);
     }
     dst(h, i, out);
   }
@@ -118,9 +132,11 @@ __global__ void __launch_bounds__(THREADS) qkv_finish_kernel(WideArgs a, int* er
   // queries
   float rstd = 1.f;
   if (a.scope == 2 && a.q_gain != nullptr)
-    rstd = 1.0f / sqrtf(block_sumsq<T>(row, a.nq * a.d, scratch) / (float)(a.nq * a.d) + a.eps);
+    rstd = 1.0f / sqrtf(block_sumsq<T>(a, row, 0, a.nq * a.d, scratch) / (float)(a.nq * a.d) + a.eps);
   T* q_dst = reinterpret_cast<T*>(a.q_out) + (int64_t)t * a.nq * a.D;
-  finish_heads<T>(a, row, a.nq, a.q_gain, rstd, cs, sn, head_rstd,
+  const float temperature =
+      a.temp_coef != 0.f ? 1.0f + a.temp_coef * logf((float)((pos + 1) / a.temp_every + 1)) : 1.0f;
+  finish_heads<T>(a, row, 0, a.nq, a.q_gain, rstd, cs, sn, head_rstd, temperature,
                   [&](int h, int i, float v) { q_dst[h * a.D + i] = ls_from_float<T>(v); });
   if (!a.has_kv || !a.write_cache) return;
 
@@ -138,16 +154,16 @@ __global__ void __launch_bounds__(THREADS) qkv_finish_kernel(WideArgs a, int* er
   float k_rstd = 1.f;
   if (a.scope == 2 && a.k_gain != nullptr) {
     __syncthreads();
-    k_rstd = 1.0f / sqrtf(block_sumsq<T>(k_src, a.nkv * a.d, scratch) / (float)(a.nkv * a.d) + a.eps);
+    k_rstd = 1.0f / sqrtf(block_sumsq<T>(a, k_src, a.nq * a.d, a.nkv * a.d, scratch) / (float)(a.nkv * a.d) + a.eps);
   }
   __syncthreads();          // head_rstd is used again
-  finish_heads<T>(a, k_src, a.nkv, a.k_gain, k_rstd, cs, sn, head_rstd, [&](int h, int i, float v) {
+  finish_heads<T>(a, k_src, a.nq * a.d, a.nkv, a.k_gain, k_rstd, cs, sn, head_rstd, 1.0f, [&](int h, int i, float v) {
     pages[((((int64_t)page * 2 + 0) * a.nkv + h) * a.page_size + in_page) * a.D + i] = ls_from_float<T>(v);
   });
   for (int e = threadIdx.x; e < a.nkv * a.D; e += THREADS) {
     const int h = e / a.D, i = e - h * a.D;
     pages[((((int64_t)page * 2 + 1) * a.nkv + h) * a.page_size + in_page) * a.D + i] =
-        i < a.dv ? v_src[h * a.dv + i] : ls_from_float<T>(0.f);
+        i < a.dv ? ls_from_float<T>(biased_at<T>(a, v_src, (a.nq + a.nkv) * a.d, h * a.dv + i)) : ls_from_float<T>(0.f);
   }
 }
 
@@ -158,6 +174,7 @@ LS_API int ls_qkv_finish(const void* qkv, int64_t ld, void* q_out, void* pages, 
                          const int* positions, const int* token_req, const int* block_table, int table_stride,
                          int tokens, int nq, int nkv, int d, int dv, int D, int rot_dim, int page_size,
                          int num_pages, int max_positions, float eps, int scope, int has_kv, int write_cache,
+                         const void* bias, int bias_dtype, float temp_coef, int temp_every,
                          int* err, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (nq <= 0 || nkv <= 0 || d <= 0 || dv <= 0 || D < d || D < dv || scope < 0 || scope > 2) return LS_E_SIZE;
@@ -165,7 +182,10 @@ LS_API int ls_qkv_finish(const void* qkv, int64_t ld, void* q_out, void* pages, 
   if (scope == 1 && (nq > 256 || nkv > 256)) return LS_E_SIZE;
   if (gain_dtype != LS_F32 && gain_dtype != LS_BF16) return LS_E_DTYPE;
   if (write_cache && (pages == nullptr || page_size <= 0)) return LS_E_SIZE;
+  if (temp_coef != 0.f && temp_every <= 0) return LS_E_SIZE;
+  if (bias != nullptr && bias_dtype != LS_F32 && bias_dtype != LS_BF16) return LS_E_DTYPE;
   WideArgs a;
+  a.bias = bias; a.bias_bf16 = bias_dtype == LS_BF16 ? 1 : 0; a.temp_coef = temp_coef; a.temp_every = temp_every > 0 ? temp_every : 1;
   a.qkv = qkv; a.q_out = q_out; a.pages = pages; a.q_gain = q_gain; a.k_gain = k_gain;
   a.cos_table = cos_table; a.sin_table = sin_table; a.positions = positions; a.token_req = token_req;
   a.block_table = block_table; a.ld = ld; a.gain_bf16 = gain_dtype == LS_BF16 ? 1 : 0;

@@ -172,6 +172,15 @@ __global__ void __launch_bounds__(PREP_THREADS) double_exp_decay_kernel(float* _
   if (i < count) z[i] = expf(-expf(z[i] + bias[i % channels]));
 }
 
+// z <- sigmoid(z + bias[column])^(1 / tau), element by element, through its logarithm:
+// exp(-softplus(-(z + bias)) / tau)
+__global__ void __launch_bounds__(PREP_THREADS) sigmoid_power_decay_kernel(float* __restrict__ z, const float* __restrict__ bias,
+                                                                           int64_t count, int channels, float inv_tau) {
+  ls_dependency_sync();
+  const int64_t i = (int64_t)blockIdx.x * PREP_THREADS + threadIdx.x;
+  if (i < count) z[i] = expf(-softplus_f(-(z[i] + bias[i % channels])) * inv_tau);
+}
+
 // ---------------------------------------------------------------------------------------
 // token shift: five mixes of a token with the one before it (the carried one at a portion's start)
 // ---------------------------------------------------------------------------------------
@@ -207,7 +216,8 @@ __global__ void __launch_bounds__(PREP_THREADS) tanh_kernel(T* __restrict__ x, i
 // ---------------------------------------------------------------------------------------
 constexpr int ROWS = 16;          // key channels of a column that one thread keeps in registers
 constexpr int CHUNK = 8;          // tokens staged in shared memory at a time
-enum { RULE_DELTA = 0, RULE_WKV = 1 };
+// RULE_GLA: a decayed sum of outer products, S <- diag(decay_t) S + k_t v_t^T, o_t = out_scale S^T q_t
+enum { RULE_DELTA = 0, RULE_WKV = 1, RULE_GLA = 2 };
 
 struct RuleArgs {
   const int* portions;     // from find_portions_kernel
@@ -228,6 +238,8 @@ struct RuleArgs {
   int carry_width;         // delta: C; wkv: width
   int carry_rows;          // delta: taps - 1; wkv: 1
   int H, G, dk, dv, lanes; // lanes: threads that share a column (a power of two, lanes * ROWS >= dk)
+  int64_t in_ld;           // gla: q, k, v are columns of wider rows, this many elements apart
+  float out_scale;         // gla: factor on the read-out (the queries' scale)
 };
 
 // One staged value's source: where token t's copy lies (p + t * stride), and its element type.
@@ -292,7 +304,7 @@ __global__ void __launch_bounds__(128) rule_kernel(RuleArgs a) {
         s.kind = 1;
       } else {
         s.p = reinterpret_cast<const char*>(reinterpret_cast<const T*>(which == 0 ? a.in_a : a.in_b) + h * dk + i);
-        s.stride = (int64_t)a.H * dk * sizeof(T);
+        s.stride = (RULE == RULE_GLA ? a.in_ld : (int64_t)a.H * dk) * sizeof(T);
         s.kind = 2;
       }
     } else if (k < 3 * dk + CB) {
@@ -304,7 +316,7 @@ __global__ void __launch_bounds__(128) rule_kernel(RuleArgs a) {
           s.kind = 1;
         } else {
           s.p = reinterpret_cast<const char*>(reinterpret_cast<const T*>(a.in_v) + h * dv + j);
-          s.stride = (int64_t)a.H * dv * sizeof(T);
+          s.stride = (RULE == RULE_GLA ? a.in_ld : (int64_t)a.H * dv) * sizeof(T);
           s.kind = 2;
         }
       }
@@ -352,6 +364,15 @@ __global__ void __launch_bounds__(128) rule_kernel(RuleArgs a) {
           S[4 * r + 2] = fmaf(kk[r].z, u, S[4 * r + 2]); o2 = fmaf(S[4 * r + 2], qq.z, o2);
           S[4 * r + 3] = fmaf(kk[r].w, u, S[4 * r + 3]); o3 = fmaf(S[4 * r + 3], qq.w, o3);
         }
+      } else if (RULE == RULE_GLA) {
+#pragma unroll
+        for (int r = 0; r < ROWS / 4; ++r) {
+          const float4 qq = A[r], kk = B[r], dd = D[r];
+          S[4 * r] = fmaf(dd.x, S[4 * r], kk.x * vj); o0 = fmaf(qq.x, S[4 * r], o0);
+          S[4 * r + 1] = fmaf(dd.y, S[4 * r + 1], kk.y * vj); o1 = fmaf(qq.y, S[4 * r + 1], o1);
+          S[4 * r + 2] = fmaf(dd.z, S[4 * r + 2], kk.z * vj); o2 = fmaf(qq.z, S[4 * r + 2], o2);
+          S[4 * r + 3] = fmaf(dd.w, S[4 * r + 3], kk.w * vj); o3 = fmaf(qq.w, S[4 * r + 3], o3);
+        }
       } else {
 #pragma unroll
         for (int r = 0; r < ROWS / 4; ++r) {
@@ -368,6 +389,7 @@ __global__ void __launch_bounds__(128) rule_kernel(RuleArgs a) {
       }
       float o = (o0 + o1) + (o2 + o3);
       for (int off = L >> 1; off > 0; off >>= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+      if (RULE == RULE_GLA) o *= a.out_scale;
       if (active && part == 0) a.out[(int64_t)(t0 + c0 + tt) * a.H * dv + h * dv + col] = o;
     }
   };
@@ -452,7 +474,7 @@ __global__ void __launch_bounds__(128) rule_kernel(RuleArgs a) {
     }
   }
   // the rest of the state: the last inputs of this portion, behind those that were carried
-  if (blockIdx.y == 0 && blockIdx.z == 0) {
+  if (blockIdx.y == 0 && blockIdx.z == 0 && a.carry_rows > 0) {
     float* carried = a.state + (int64_t)slot * a.state_stride + (int64_t)a.H * dk * dv;
     const T* src = reinterpret_cast<const T*>(a.carry_src);
     const int rows = a.carry_rows, W = a.carry_width;
@@ -477,7 +499,8 @@ template <typename T>
 __global__ void __launch_bounds__(PREP_THREADS) head_rms_gate_kernel(const float* __restrict__ o, const float* __restrict__ gain,
                                                                      const float* __restrict__ gate_f32,
                                                                      const T* __restrict__ gate_x, T* __restrict__ out,
-                                                                     int H, int dv, int gain_shared, int gate_mode, float eps) {
+                                                                     int H, int dv, int gain_shared, int gate_mode, float eps,
+                                                                     int64_t gate_ld) {
   ls_dependency_sync();
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int h = warp; h < H; h += PREP_THREADS / 32) {
@@ -491,7 +514,7 @@ __global__ void __launch_bounds__(PREP_THREADS) head_rms_gate_kernel(const float
     const float rstd = 1.0f / sqrtf(ss / (float)dv + eps);
     for (int j = lane; j < dv; j += 32) {
       const float gt = gate_mode == 0 ? gate_f32[base + j]
-                       : gate_mode == 2 ? sigmoid_f(gate_f32[base + j]) : silu_f(ls_to_float<T>(gate_x[base + j]));
+                       : gate_mode == 2 ? sigmoid_f(gate_f32[base + j]) : silu_f(ls_to_float<T>(gate_x[(int64_t)t * gate_ld + h * dv + j]));
       out[base + j] = ls_from_float<T>(o[base + j] * rstd * gain[gain_shared ? j : h * dv + j] * gt);
     }
   }
@@ -580,10 +603,22 @@ LS_API int ls_tanh_rows(void* x, int dtype, long long count, cudaStream_t stream
 
 // rule 0: the gated delta rule; rule 1: the wkv rule.  `dtype`: the engine's type (of r, k, v for
 // rule 1, and of carry_src for both).
+LS_API int ls_sigmoid_power_decay(float* z, const float* bias, long long count, int channels, float tau, cudaStream_t stream) {
+  if (count <= 0) return 0;
+  if (channels <= 0 || !(tau > 0.f)) return LS_E_SIZE;
+  LS_COUNT(LS_K_SIGMOID_POWER_DECAY);
+  const dim3 grid((unsigned)((count + PREP_THREADS - 1) / PREP_THREADS));
+  cudaError_t e = ls_launch(sigmoid_power_decay_kernel, grid, dim3(PREP_THREADS), 0, stream, z, bias, (int64_t)count, channels,
+                            1.0f / tau);
+  if (e != cudaSuccess) return (int)e;
+  return ls_launch_status();
+}
+
 LS_API int ls_state_rule(int rule, int dtype, const int* portions, int max_portions, float* state, int64_t state_stride,
                          const void* in_a, const void* in_b, const void* in_v, const float* decay,
                          const float* beta, const float* bonus, float* out, const void* carry_src, int64_t carry_ld, int carry_width,
-                         int carry_rows, int H, int G, int dk, int dv, cudaStream_t stream) {
+                         int carry_rows, int H, int G, int dk, int dv, int64_t in_ld, float out_scale,
+                         cudaStream_t stream) {
   if (max_portions <= 0) return 0;
   if (H <= 0 || G <= 0 || H % G || dk <= 0 || dk > 32 * ROWS || dv <= 0 || carry_rows < 0 || carry_rows >= MAX_TAPS) return LS_E_SIZE;
   if (H > 65535) return LS_E_SIZE;
@@ -592,6 +627,7 @@ LS_API int ls_state_rule(int rule, int dtype, const int* portions, int max_porti
   a.decay = decay; a.beta = beta; a.bonus = bonus; a.out = out; a.carry_src = carry_src; a.carry_ld = carry_ld;
   a.carry_width = carry_width; a.carry_rows = carry_rows; a.H = H; a.G = G; a.dk = dk; a.dv = dv;
   a.lanes = lanes_for(dk);
+  a.in_ld = in_ld; a.out_scale = out_scale;
   // columns a block: as many as fill 128 threads, fewer where the head has fewer
   int threads = 128;
   while (threads > 32 && (threads / 2) / a.lanes >= dv) threads /= 2;
@@ -605,7 +641,9 @@ LS_API int ls_state_rule(int rule, int dtype, const int* portions, int max_porti
     if (cudaFuncSetAttribute(rule_kernel<RULE_DELTA, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) != cudaSuccess ||
         cudaFuncSetAttribute(rule_kernel<RULE_DELTA, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) != cudaSuccess ||
         cudaFuncSetAttribute(rule_kernel<RULE_WKV, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) != cudaSuccess ||
-        cudaFuncSetAttribute(rule_kernel<RULE_WKV, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) != cudaSuccess)
+        cudaFuncSetAttribute(rule_kernel<RULE_WKV, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) != cudaSuccess ||
+        cudaFuncSetAttribute(rule_kernel<RULE_GLA, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) != cudaSuccess ||
+        cudaFuncSetAttribute(rule_kernel<RULE_GLA, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) != cudaSuccess)
       return LS_E_SMEM;
     configured = true;
   }
@@ -621,6 +659,12 @@ LS_API int ls_state_rule(int rule, int dtype, const int* portions, int max_porti
     if (dtype == LS_F32) e = ls_launch(rule_kernel<RULE_WKV, float>, grid, dim3(threads), smem, stream, a);
     else if (dtype == LS_BF16) e = ls_launch(rule_kernel<RULE_WKV, __nv_bfloat16>, grid, dim3(threads), smem, stream, a);
     else return LS_E_DTYPE;
+  } else if (rule == RULE_GLA) {
+    if (H != G || in_ld <= 0) return LS_E_SIZE;
+    LS_COUNT(LS_K_GLA_RULE);
+    if (dtype == LS_F32) e = ls_launch(rule_kernel<RULE_GLA, float>, grid, dim3(threads), smem, stream, a);
+    else if (dtype == LS_BF16) e = ls_launch(rule_kernel<RULE_GLA, __nv_bfloat16>, grid, dim3(threads), smem, stream, a);
+    else return LS_E_DTYPE;
   } else return LS_E_SIZE;
   if (e != cudaSuccess) return (int)e;
   return ls_launch_status();
@@ -629,18 +673,19 @@ LS_API int ls_state_rule(int rule, int dtype, const int* portions, int max_porti
 // gate_logit: gate_f32 holds logits, the gate is their sigmoid
 LS_API int ls_head_rms_gate(const float* o, const float* gain, const float* gate_f32, const void* gate_x, void* out,
                             int dtype, int tokens, int H, int dv, int gain_shared, int gate_logit, float eps,
-                            cudaStream_t stream) {
+                            int64_t gate_ld, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (H <= 0 || dv <= 0 || (gate_f32 == nullptr) == (gate_x == nullptr)) return LS_E_SIZE;
   const int mode = gate_f32 != nullptr ? (gate_logit ? 2 : 0) : 1;
+  if (gate_ld <= 0) gate_ld = (int64_t)H * dv;       // the gate's rows lie one after the other
   LS_COUNT(LS_K_HEAD_RMS_GATE);
   cudaError_t e;
   if (dtype == LS_F32)
     e = ls_launch(head_rms_gate_kernel<float>, dim3(tokens), dim3(PREP_THREADS), 0, stream, o, gain, gate_f32,
-                  (const float*)gate_x, (float*)out, H, dv, gain_shared, mode, eps);
+                  (const float*)gate_x, (float*)out, H, dv, gain_shared, mode, eps, gate_ld);
   else if (dtype == LS_BF16)
     e = ls_launch(head_rms_gate_kernel<__nv_bfloat16>, dim3(tokens), dim3(PREP_THREADS), 0, stream, o, gain, gate_f32,
-                  (const __nv_bfloat16*)gate_x, (__nv_bfloat16*)out, H, dv, gain_shared, mode, eps);
+                  (const __nv_bfloat16*)gate_x, (__nv_bfloat16*)out, H, dv, gain_shared, mode, eps, gate_ld);
   else return LS_E_DTYPE;
   if (e != cudaSuccess) return (int)e;
   return ls_launch_status();

@@ -129,8 +129,14 @@ class ModelRunner:
                 return model.head.forward(model.final_norm.forward(h, ctx.wanted_rows))
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
 
+        def add_embedding(h, ctx):
+            model.embedding.accumulate(h, ctx)
+            return h
+
         program = [(bool(model.embedding.graph_safe), embed)]
         for run in self.spec.schedule:
+            if run.add_embedding:
+                program.append((bool(model.embedding.graph_safe), add_embedding))
             for safe, fn in model.blocks[run.layer].steps():
                 program.append((bool(safe), layer_step(fn, run)))
         program.append((bool(model.final_norm.graph_safe and model.head.graph_safe), finish))

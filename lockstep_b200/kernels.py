@@ -44,9 +44,13 @@ class KernelError(RuntimeError):
 
 _SIGNATURES = {
     "core": {
-        "ls_embed_gather": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+        "ls_embed_gather": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
         "ls_rmsnorm": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
-                       c_float, c_void_p, c_void_p],
+                       c_float, c_int, c_void_p, c_void_p],
+        "ls_clamped_glu": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_float,
+                           c_void_p, c_void_p, c_int, c_void_p],
+        "ls_row_bias": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "ls_weighted_sum": [c_void_p, c_void_p, ctypes.c_longlong, c_int, ctypes.POINTER(c_float), c_void_p],
         "ls_qk_norm_rope_store": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
                                   c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                   c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
@@ -57,12 +61,12 @@ _SIGNATURES = {
         "ls_attention_split_size": [],
         "ls_attention_tile": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                               c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                              c_float, c_void_p, c_void_p, c_void_p],
+                              c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
         "ls_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-                                c_void_p, c_void_p, c_void_p],
+                                c_void_p, c_void_p, c_void_p, c_void_p],
         "ls_attention_combine": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
-                                 c_void_p],
+                                 c_void_p, c_void_p],
         "ls_argmax": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
         "ls_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                       c_int, c_void_p],
@@ -90,7 +94,13 @@ _SIGNATURES["tc"] = {
 _SIGNATURES["seq"] = {
     "ls_qkv_finish": [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                       c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                      c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p],
+                      c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_int, c_float, c_int, c_void_p, c_void_p],
+    "ls_latent_finish": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                         c_int, c_float, c_void_p, c_void_p],
+    "ls_heads_product": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int,
+                         c_void_p],
+    "ls_sigmoid_power_decay": [c_void_p, c_void_p, ctypes.c_longlong, c_int, c_float, c_void_p],
     "ls_find_portions": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p],
     "ls_delta_prep": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
                       c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
@@ -99,9 +109,9 @@ _SIGNATURES["seq"] = {
                      c_void_p],
     "ls_state_rule": [c_int, c_int, c_void_p, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
                       c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int,
-                      c_void_p],
+                      c_int64, c_float, c_void_p],
     "ls_head_rms_gate": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                         c_float, c_void_p],
+                         c_float, c_int64, c_void_p],
     "ls_tanh_rows": [c_void_p, c_int, ctypes.c_longlong, c_void_p],
     "ls_experts_tile_rows": [],
     "ls_experts_route": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
@@ -247,19 +257,25 @@ def attention_split_size() -> int:
     return int(library().ls_attention_split_size())
 
 
-def embed_gather(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err: torch.Tensor) -> None:
+def embed_gather(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err: torch.Tensor,
+                 accumulate: bool = False) -> None:
+    """out[t] = table[ids[t]] (float32), or out[t] += table[ids[t]] with ``accumulate``."""
     tokens, width = out.shape
     if ids.numel() != tokens or table.shape[1] != width:
         raise KernelError("embed_gather: shapes do not agree")
     _check(library().ls_embed_gather(
         _dev(ids, "ids", torch.int32), _dev(table, "table"), _code(table),
-        _dev(out, "out", torch.float32), tokens, width, table.shape[0], _dev(err, "err", torch.int32),
-        _stream()), "embed_gather")
+        _dev(out, "out", torch.float32), tokens, width, table.shape[0], 1 if accumulate else 0,
+        _dev(err, "err", torch.int32), _stream()), "embed_gather")
 
 
 def rmsnorm(x: torch.Tensor, gain: torch.Tensor, out: torch.Tensor, eps: float, err: torch.Tensor,
-            row_index: torch.Tensor | None = None) -> None:
+            row_index: torch.Tensor | None = None, groups: int = 1) -> None:
+    """``groups`` > 1: a row is cut into that many equal consecutive parts, each divided by its
+    own root mean square; the gain runs over the whole row."""
     rows, width = out.shape
+    if groups < 1 or width % groups:
+        raise KernelError(f"rmsnorm: a row of {width} elements cannot be cut into {groups} equal parts")
     if x.shape[1] != width or gain.numel() != width:
         raise KernelError("rmsnorm: shapes do not agree")
     if row_index is None and x.shape[0] != rows:
@@ -268,7 +284,7 @@ def rmsnorm(x: torch.Tensor, gain: torch.Tensor, out: torch.Tensor, eps: float, 
         raise KernelError("rmsnorm: row_index does not match the output rows")
     _check(library().ls_rmsnorm(
         _dev(x, "x", torch.float32), _opt(row_index, "row_index", torch.int32), _dev(gain, "gain"),
-        _code(gain), _dev(out, "out"), _code(out), rows, width, x.shape[0], float(eps),
+        _code(gain), _dev(out, "out"), _code(out), rows, width, x.shape[0], float(eps), int(groups),
         _dev(err, "err", torch.int32), _stream()), "rmsnorm")
 
 
@@ -316,6 +332,45 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
                                  _stream()), "silu_mul")
 
 
+def clamped_glu(gate_up, bias, out, limit: float, alpha: float, residual=None, residual_bias=None) -> None:
+    """out = g sigmoid(alpha g) (u + 1) with g = min(gate + b, limit), u = clamp(up + b, -limit, limit), from
+    ``gate_up`` [rows, 2 width] (gate columns, then up columns; float32 or the type of ``out``) and ``bias``
+    [2 width] or None.  With ``residual`` (float32 [rows, w]) and ``residual_bias`` [w] the same launch adds the
+    bias of the projection that follows into the residual stream."""
+    rows, width = out.shape
+    if gate_up.shape != (rows, 2 * width) or (bias is not None and bias.numel() != 2 * width):
+        raise KernelError("clamped_glu: shapes do not agree")
+    if (residual is None) != (residual_bias is None) or \
+            (residual is not None and (residual.shape[0] != rows or residual_bias.numel() != residual.shape[1])):
+        raise KernelError("clamped_glu: the residual stream and its bias do not agree")
+    if bias is not None and residual_bias is not None and bias.dtype != residual_bias.dtype:
+        raise KernelError("clamped_glu: biases of two element types")
+    some = bias if bias is not None else residual_bias
+    _check(library().ls_clamped_glu(
+        _dev(gate_up, "gate_up"), _code(gate_up), _opt(bias, "bias"), _code(some) if some is not None else F32,
+        _dev(out, "out"), _code(out), rows, width, float(limit), float(alpha), _opt(residual, "residual", torch.float32),
+        _opt(residual_bias, "residual_bias"), residual.shape[1] if residual is not None else 0, _stream()), "clamped_glu")
+
+
+def row_bias(x, bias, add: bool = False) -> None:
+    """Every row of ``x`` (float32 [rows, width]) set to ``bias`` (to zero for None), or ``bias`` added to it."""
+    rows, width = x.shape
+    if bias is not None and bias.numel() != width:
+        raise KernelError("row_bias: the bias does not match the rows")
+    _check(library().ls_row_bias(_dev(x, "x", torch.float32), _opt(bias, "bias"), _code(bias) if bias is not None else F32,
+                                 rows, width, 1 if add else 0, _stream()), "row_bias")
+
+
+def weighted_sum(residual, branches, scales) -> None:
+    """residual += sum_b scales[b] * branches[b]; ``branches`` float32 [n, *residual.shape]."""
+    n = branches.shape[0]
+    if tuple(branches.shape[1:]) != tuple(residual.shape) or len(scales) != n:
+        raise KernelError("weighted_sum: shapes do not agree")
+    _check(library().ls_weighted_sum(_dev(residual, "residual", torch.float32), _dev(branches, "branches", torch.float32),
+                                     residual.numel(), n, (c_float * n)(*[float(v) for v in scales]), _stream()),
+           "weighted_sum")
+
+
 def _rows(t: torch.Tensor, name: str) -> tuple[int, int]:
     """(pointer, row pitch in elements) of a 2-D operand whose rows are contiguous: a whole
     tensor, or a view of some columns of one."""
@@ -347,25 +402,29 @@ def _slopes(slopes, nq: int) -> int:
 
 
 def attention_tile(q, pages, out, part_acc, part_ml, work, n_work, block_table, nq, nkv, d,
-                   window, scale, err, slopes=None) -> None:
+                   window, scale, err, slopes=None, log_rates=None, sinks=None) -> None:
     """``slopes`` (float32 [nq] or None): slopes[head] x (key position - query position) is added
-    to every score."""
+    to every score; with ``log_rates`` [nq] as well, slopes[head] x ln(1 + log_rates[head] x (query
+    position - key position)) is taken off instead.  ``sinks`` [nq]: exp(sinks[head]) is one more
+    term of the softmax's denominator (rows that write ``out``; partials get theirs in
+    ``attention_combine``)."""
     _check(library().ls_attention_tile(
         _dev(q, "q"), _dev(pages, "pages", q.dtype), _opt(out, "out", q.dtype),
         _opt(part_acc, "part_acc", torch.float32), _opt(part_ml, "part_ml", torch.float32), _code(q),
         _dev(work, "work", torch.int32), n_work, _dev(block_table, "block_table", torch.int32),
         block_table.shape[-1], nq, nkv, d, pages.shape[3], pages.shape[0], int(window), float(scale),
-        _slopes(slopes, nq), _dev(err, "err", torch.int32), _stream()), "attention_tile")
+        _slopes(slopes, nq), _slopes(log_rates, nq), _slopes(sinks, nq), _dev(err, "err", torch.int32),
+        _stream()), "attention_tile")
 
 
 def attention_decode(q, pages, part_acc, part_ml, work, n_work, block_table, nq, nkv, d, window,
-                     scale, err, slopes=None) -> bool:
+                     scale, err, slopes=None, log_rates=None) -> bool:
     """Returns False (and launches nothing) for shapes the decode kernel does not take."""
     status = library().ls_attention_decode(
         _dev(q, "q"), _dev(pages, "pages", q.dtype), _dev(part_acc, "part_acc", torch.float32),
         _dev(part_ml, "part_ml", torch.float32), _code(q), _dev(work, "work", torch.int32), n_work,
         _dev(block_table, "block_table", torch.int32), block_table.shape[-1], nq, nkv, d,
-        pages.shape[3], pages.shape[0], int(window), float(scale), _slopes(slopes, nq),
+        pages.shape[3], pages.shape[0], int(window), float(scale), _slopes(slopes, nq), _slopes(log_rates, nq),
         _dev(err, "err", torch.int32), _stream())
     if status == -2:
         return False
@@ -412,11 +471,11 @@ def attention_prefill_tc(q, pages, out, work, n_work, block_table, nq, nkv, d, w
     return True
 
 
-def attention_combine(part_acc, part_ml, out, items, n_items, nq, d) -> None:
+def attention_combine(part_acc, part_ml, out, items, n_items, nq, d, sinks=None) -> None:
     _check(library().ls_attention_combine(
         _dev(part_acc, "part_acc", torch.float32), _dev(part_ml, "part_ml", torch.float32),
-        _dev(out, "out"), _code(out), _dev(items, "items", torch.int32), n_items, nq, d, _stream()),
-        "attention_combine")
+        _dev(out, "out"), _code(out), _dev(items, "items", torch.int32), n_items, nq, d, _slopes(sinks, nq),
+        _stream()), "attention_combine")
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
@@ -569,16 +628,18 @@ def gemm_nt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = E
 # library "seq": heads of unequal sizes, mixers with a carried state, routed experts
 # ---------------------------------------------------------------------------
 
-RULE_DELTA, RULE_WKV = 0, 1
+RULE_DELTA, RULE_WKV, RULE_GLA = 0, 1, 2
 
 
 def qkv_finish(qkv, q_out, pages, q_gain, k_gain, cos, sin, positions, token_req, block_table, nq: int, nkv: int,
                d: int, dv: int, pad: int, rot_dim: int, eps: float, whole_projection: bool, has_kv: bool,
-               write_cache: bool, err) -> None:
+               write_cache: bool, err, bias=None, q_temp=None) -> None:
     """Finishes a projection ``qkv`` [tokens, nq*d (+ nkv*d + nkv*dv)]: RMSNorm of q and of k (over
     the whole projection, or per head), rotation of the first ``rot_dim`` elements of each head,
     queries to ``q_out`` [tokens, nq*pad] and keys and values into ``pages``
-    [num_pages, 2, nkv, page_size, pad], padded with zeros (csrc/heads_wide.cu)."""
+    [num_pages, 2, nkv, page_size, pad], padded with zeros (csrc/heads_wide.cu).  ``bias`` (one
+    element per column of ``qkv``, or None) is added first; ``q_temp`` = (coef, every): the query at
+    position p is multiplied by 1 + coef ln(floor((p + 1) / every) + 1)."""
     tokens = qkv.shape[0]
     cols = nq * d + (nkv * (d + dv) if has_kv else 0)
     if qkv.shape[1] != cols or q_out.shape != (tokens, nq * pad) or q_out.dtype != qkv.dtype:
@@ -598,6 +659,9 @@ def qkv_finish(qkv, q_out, pages, q_gain, k_gain, cos, sin, positions, token_req
         num_pages, page_size = 0, 1
     if rot_dim and (cos.shape != sin.shape or cos.shape[1] != rot_dim // 2):
         raise KernelError("qkv_finish: rotary tables do not match rot_dim")
+    if bias is not None and bias.numel() != cols:
+        raise KernelError("qkv_finish: the bias does not match the projection")
+    coef, every = (float(q_temp[0]), int(q_temp[1])) if q_temp else (0.0, 1)
     _check(library("seq").ls_qkv_finish(
         _dev(qkv, "qkv"), qkv.shape[1], _dev(q_out, "q_out"), _opt(pages if write_cache else None, "pages"),
         _code(qkv), _opt(q_gain, "q_gain"), _opt(k_gain, "k_gain"), _code(gains[0]) if gains else F32,
@@ -605,7 +669,53 @@ def qkv_finish(qkv, q_out, pages, q_gain, k_gain, cos, sin, positions, token_req
         _dev(positions, "positions", torch.int32), _dev(token_req, "token_req", torch.int32),
         _dev(block_table, "block_table", torch.int32), block_table.shape[-1], tokens, nq, nkv, d, dv, pad, rot_dim,
         page_size, num_pages, cos.shape[0] if rot_dim else 0, float(eps), 2 if whole_projection else 1,
-        1 if has_kv else 0, 1 if write_cache else 0, _dev(err, "err", torch.int32), _stream()), "qkv_finish")
+        1 if has_kv else 0, 1 if write_cache else 0, _opt(bias, "bias"), _code(bias) if bias is not None else F32,
+        coef, every, _dev(err, "err", torch.int32), _stream()), "qkv_finish")
+
+
+def latent_finish(proj, q_out, pages, gain, cos, sin, positions, token_req, block_table, heads: int, d: int, dr: int,
+                  rank: int, pad: int, eps: float, interleaved: bool, write_cache: bool, err) -> None:
+    """Between the projections and the attention over a cached latent (csrc/latent.cu).  ``proj`` [tokens, >=
+    heads (d + dr) + rank + dr]: every head's plain and rotated query part, then the latent and the shared
+    rotated key part.  Writes the rotated query parts (and the padding) to columns rank .. pad of every head of
+    ``q_out`` [tokens, heads pad], and [norm(latent) ; rotated key part ; 0] / [norm(latent) ; 0] as the token's
+    key and value rows into ``pages`` [num_pages, 2, 1, page_size, pad]."""
+    tokens = proj.shape[0]
+    if q_out.shape != (tokens, heads * pad) or q_out.dtype != proj.dtype or gain.numel() != rank:
+        raise KernelError("latent_finish: shapes do not agree")
+    if write_cache and (pages.dtype != proj.dtype or tuple(pages.shape[1:3]) != (2, 1) or pages.shape[4] != pad):
+        raise KernelError("latent_finish: cache pages do not match")
+    if dr and (cos.shape != sin.shape or cos.shape[1] != dr // 2):
+        raise KernelError("latent_finish: rotary tables do not match the rotated part")
+    pp, ld = _rows(proj, "proj")
+    _check(library("seq").ls_latent_finish(
+        pp, ld, _code(proj), _dev(q_out, "q_out"), _opt(pages if write_cache else None, "pages"), _dev(gain, "gain"),
+        _code(gain), _opt(cos if dr else None, "cos", torch.float32), _opt(sin if dr else None, "sin", torch.float32),
+        _dev(positions, "positions", torch.int32), _dev(token_req, "token_req", torch.int32),
+        _dev(block_table, "block_table", torch.int32), block_table.shape[-1], tokens, heads, d, dr, rank, pad,
+        pages.shape[3] if write_cache else 1, pages.shape[0] if write_cache else 0, cos.shape[0] if dr else 0,
+        1 if interleaved else 0, 1 if write_cache else 0, float(eps), _dev(err, "err", torch.int32), _stream()),
+        "latent_finish")
+
+
+def heads_product(a, a_head_stride: int, w, out, out_head_stride: int) -> None:
+    """out[t, h out_head_stride + n] = sum_k a[t, h a_head_stride + k] w[h, n, k] for every head h at once:
+    ``a`` and ``out`` are [tokens, columns] (views of some columns of wider tensors are fine), ``w`` [heads, n, k]."""
+    heads, n, k = w.shape
+    ap, a_ld = _rows(a, "a")
+    op, o_ld = _rows(out, "out")
+    if a.shape[0] != out.shape[0] or a.dtype != w.dtype or out.dtype != w.dtype:
+        raise KernelError("heads_product: shapes or types do not agree")
+    if (heads - 1) * a_head_stride + k > a.shape[1] or (heads - 1) * out_head_stride + n > out.shape[1]:
+        raise KernelError("heads_product: the heads do not fit the rows")
+    _check(library("seq").ls_heads_product(ap, a_ld, a_head_stride, _dev(w, "w"), op, o_ld, out_head_stride, _code(w),
+                                           a.shape[0], heads, n, k, _stream()), "heads_product")
+
+
+def sigmoid_power_decay(z, bias, tau: float) -> None:
+    """z <- sigmoid(z + bias)^(1 / tau) in place (float32 [tokens, channels]), through its logarithm."""
+    _check(library("seq").ls_sigmoid_power_decay(_dev(z, "z", torch.float32), _dev(bias, "bias", torch.float32),
+                                                 z.numel(), z.shape[1], float(tau), _stream()), "sigmoid_power_decay")
 
 
 def find_portions(token_slot, out, cap: int, err) -> None:
@@ -658,25 +768,42 @@ def tanh_rows(x) -> None:
 
 
 def state_rule(rule: int, dtype, portions, max_portions: int, state, in_a, in_b, in_v, decay, beta, bonus, out,
-               carry_src, carry_width: int, carry_rows: int, heads: int, groups: int, dk: int, dv: int) -> None:
-    """Walks every portion of the step through a state rule (RULE_DELTA, RULE_WKV), reading and
-    writing ``state[slot]`` (float32: the matrix state, then the carried inputs)."""
+               carry_src, carry_width: int, carry_rows: int, heads: int, groups: int, dk: int, dv: int,
+               out_scale: float = 1.0) -> None:
+    """Walks every portion of the step through a state rule (RULE_DELTA, RULE_WKV, RULE_GLA), reading and
+    writing ``state[slot]`` (float32: the matrix state, then the carried inputs).  RULE_GLA (S <- diag(decay) S
+    + k v^T, o = out_scale S^T q) carries nothing else; its ``in_a``, ``in_b``, ``in_v`` (q, k, v in the engine's
+    type) may be views of columns of one wider tensor."""
+    in_ld = 0
+    if rule == RULE_GLA:
+        (pa, in_ld), (pb, ldb), (pv, ldv) = _rows(in_a, "in_a"), _rows(in_b, "in_b"), _rows(in_v, "in_v")
+        if not (in_ld == ldb == ldv) or not (in_a.dtype == in_b.dtype == in_v.dtype == dtype):
+            raise KernelError("state_rule: q, k and v must be columns of rows of one pitch, in the engine's type")
+    else:
+        pa, pb, pv = _dev(in_a, "in_a"), _opt(in_b, "in_b"), _opt(in_v, "in_v")
     _check(library("seq").ls_state_rule(
         rule, _DTYPE_CODE[dtype], _dev(portions, "portions", torch.int32), max_portions,
-        _dev(state, "state", torch.float32), state.shape[1], _dev(in_a, "in_a"), _opt(in_b, "in_b"), _opt(in_v, "in_v"),
+        _dev(state, "state", torch.float32), state.shape[1], pa, pb, pv,
         _dev(decay, "decay", torch.float32), _opt(beta, "beta", torch.float32), _opt(bonus, "bonus", torch.float32),
-        _dev(out, "out", torch.float32), _dev(carry_src, "carry_src", dtype), carry_src.shape[1], carry_width,
-        carry_rows, heads, groups, dk, dv, _stream()), "state_rule")
+        _dev(out, "out", torch.float32), _opt(carry_src, "carry_src", dtype),
+        carry_src.shape[1] if carry_src is not None else 0, carry_width,
+        carry_rows, heads, groups, dk, dv, in_ld, float(out_scale), _stream()), "state_rule")
 
 
 def head_rms_gate(o, gain, gate_f32, gate_x, out, heads: int, dv: int, gain_shared: bool, eps: float,
                   gate_logit: bool = False) -> None:
     """out = o / rms_per_head(o) * gain * gate, where the gate is ``gate_f32`` as it is (or its
-    sigmoid, ``gate_logit``), or silu(``gate_x``)."""
+    sigmoid, ``gate_logit``), or silu(``gate_x``); ``gate_x`` may be a view of some columns of a
+    wider tensor."""
+    gate_p, gate_ld = (0, 0)
+    if gate_x is not None:
+        if gate_x.dtype != out.dtype or gate_x.shape != (o.shape[0], heads * dv):
+            raise KernelError("head_rms_gate: the gate does not match the read-out")
+        gate_p, gate_ld = _rows(gate_x, "gate_x")
     _check(library("seq").ls_head_rms_gate(
         _dev(o, "o", torch.float32), _dev(gain, "gain", torch.float32), _opt(gate_f32, "gate_f32", torch.float32),
-        _opt(gate_x, "gate_x", out.dtype), _dev(out, "out"), _code(out), o.shape[0], heads, dv,
-        1 if gain_shared else 0, 1 if gate_logit else 0, float(eps), _stream()), "head_rms_gate")
+        gate_p, _dev(out, "out"), _code(out), o.shape[0], heads, dv,
+        1 if gain_shared else 0, 1 if gate_logit else 0, float(eps), gate_ld, _stream()), "head_rms_gate")
 
 
 def experts_tile_rows(tensor_cores: bool = False) -> int:

@@ -18,6 +18,14 @@ Further parameters, for designs that differ from that one:
 - ``borrows_kv``: the layer has no key or value tensors; the schedule gives it the cache
   entry of another layer, which it reads with its own queries, window and scale.
 - ``names``: the local names of its tensors.
+- ``bias``: the four projections have biases (``q_bias`` ... ``o_bias`` in ``names``); those of q, k
+  and v are added by the kernel that finishes the heads, the output's goes into the residual stream.
+- ``q_temp`` = {"coef": c, "every": n}: the query at position p is multiplied by
+  1 + c ln(floor((p + 1) / n) + 1).
+- ``score_bias`` "log_distance": r1[head] ln(1 + r2[head] (i - j)) is taken off the score of query i
+  with key j; r1 and r2 are tensors of the layer, one number per query head (``names``: ``r1``, ``r2``).
+- ``sink``: a learned number per query head (``names``: ``sink``) whose exponential is one more term
+  of the softmax's denominator; it has no key and no value.
 """
 
 from __future__ import annotations
@@ -30,7 +38,66 @@ from .norm import NormedRows
 
 
 _DEFAULT_NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
-                  "q_norm": "q_norm.weight", "k_norm": "k_norm.weight"}
+                  "q_norm": "q_norm.weight", "k_norm": "k_norm.weight",
+                  "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias", "o_bias": "o_proj.bias",
+                  "r1": "r1", "r2": "r2", "sink": "sink"}
+
+
+def _f32(t: torch.Tensor) -> torch.Tensor:
+    return t.to(torch.float32).contiguous()
+
+
+class ScoreExtras:
+    """What the CUDA-core attention kernels add to plain scaled scores: a bias that grows with
+    the distance of key and query (``slopes`` alone: linear; with ``log_rates``: logarithmic) and
+    sinks.  Any of them keeps the attention off the tensor-core kernels, which know none."""
+
+    def __init__(self, slopes=None, log_rates=None, sinks=None):
+        self.slopes, self.log_rates, self.sinks = slopes, log_rates, sinks
+
+    def any(self) -> bool:
+        return self.slopes is not None or self.sinks is not None
+
+
+def attend(rt: Runtime, q, ctx, cache, nq: int, nkv: int, d: int, window: int, scale: float, exact: bool,
+           extras: ScoreExtras) -> torch.Tensor:
+    """Causal attention of the step's queries ``q`` [tokens, nq d] over a layer's pages (heads of one
+    size ``d``): prompt portions by tiles, single tokens by splits and a fold.  Returns [tokens, nq d]
+    in the engine's type.  ``exact``: every row takes the tile kernel, so that a row's bits do not
+    depend on whether it was decoded or part of a prompt."""
+    t = q.shape[0]
+    tensor_core_attention = not exact and not extras.any()
+    attn = rt.rows(t, nq * d)
+    plan, done = None, False
+    if tensor_core_attention and d in (64, 128):
+        plan = ctx.attention_plan(window, K.attention_prefill_tc_tile_tokens())
+        done = not plan.n_tile or K.attention_prefill_tc(
+            q, cache.pages, attn, plan.tile_work, plan.n_tile, cache.block_table, nq, nkv, d,
+            window, scale, rt.err)
+    if not done:
+        plan = ctx.attention_plan(window)
+        if plan.n_tile:
+            K.attention_tile(q, cache.pages, attn, None, None, plan.tile_work, plan.n_tile,
+                             cache.block_table, nq, nkv, d, window, scale, rt.err, extras.slopes,
+                             extras.log_rates, extras.sinks)
+    if plan.n_split:
+        part_acc = rt.rows(plan.n_slots, nq, d, dtype=torch.float32)
+        part_ml = rt.rows(plan.n_slots, nq, 2, dtype=torch.float32)
+        done = False
+        if tensor_core_attention:
+            done = K.attention_decode_mma(q, cache.pages, part_acc, part_ml, plan.split_work,
+                                          plan.n_split, cache.block_table, nq, nkv, d, window,
+                                          scale, rt.err)
+        if not done and not exact:
+            done = K.attention_decode(q, cache.pages, part_acc, part_ml, plan.split_work,
+                                      plan.n_split, cache.block_table, nq, nkv, d, window,
+                                      scale, rt.err, extras.slopes, extras.log_rates)
+        if not done:
+            K.attention_tile(q, cache.pages, None, part_acc, part_ml, plan.split_work,
+                             plan.n_split, cache.block_table, nq, nkv, d, window,
+                             scale, rt.err, extras.slopes, extras.log_rates)
+        K.attention_combine(part_acc, part_ml, attn, plan.combine_items, plan.n_combine, nq, d, extras.sinks)
+    return attn
 
 
 class GQAttention(Mixer):
@@ -39,7 +106,7 @@ class GQAttention(Mixer):
 
     def __init__(self, hidden_size, num_heads, num_kv_heads, head_dim, scale, window, qk_norm_eps,
                  position: PositionEncoding, runtime: Runtime, value_dim=None, qk_norm_scope="head",
-                 borrows_kv=False, names=None):
+                 borrows_kv=False, names=None, bias=False, q_temp=None, score_bias=None, sink=False):
         if num_heads % num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
         if qk_norm_scope not in ("head", "projection"):
@@ -47,9 +114,17 @@ class GQAttention(Mixer):
         self.h, self.nq, self.nkv, self.d = int(hidden_size), int(num_heads), int(num_kv_heads), int(head_dim)
         self.dv = int(value_dim or head_dim)
         self.scope, self.borrows = qk_norm_scope, bool(borrows_kv)
-        # the general finishing kernel (norm over the projection, heads padded to one size) where
-        # the design asks for any of this; else the per-head kernels and the fused products
-        self.wide = self.scope == "projection" or self.dv != self.d or self.borrows or self.d % 16 != 0
+        if score_bias not in (None, "log_distance"):
+            raise ValueError(f"score_bias must be log_distance or absent, got {score_bias!r}")
+        self.bias, self.score_bias, self.sink = bool(bias), score_bias, bool(sink)
+        self.q_temp = (float(q_temp["coef"]), int(q_temp["every"])) if q_temp else None
+        if self.q_temp is not None and self.q_temp[1] <= 0:
+            raise ValueError("q_temp.every must be positive")
+        # the general finishing kernel (norm over the projection, heads padded to one size, biases,
+        # a query temperature) where the design asks for any of this; else the per-head kernels
+        # and the fused products
+        self.wide = self.scope == "projection" or self.dv != self.d or self.borrows or self.d % 16 != 0 \
+            or self.bias or self.q_temp is not None
         self.pad = -(-max(self.d, self.dv) // 16) * 16 if self.wide else self.d
         if self.pad % 16 or not 16 <= self.pad <= 256:
             raise ValueError(
@@ -59,7 +134,8 @@ class GQAttention(Mixer):
         self.scale, self.window = float(scale), int(window or 0)
         self.qk_norm_eps = qk_norm_eps
         self.position, self.rt = position, runtime
-        self.w_qkv = self.w_o = self.q_gain = self.k_gain = self.slopes = None
+        self.w_qkv = self.w_o = self.q_gain = self.k_gain = self.qkv_bias = self.o_bias = None
+        self.extras = ScoreExtras()
         # in float32 every row takes the tile kernel, so that a row's bits do not
         # depend on whether it was decoded or part of a prompt
         self.exact = runtime.dtype == torch.float32
@@ -82,6 +158,18 @@ class GQAttention(Mixer):
             specs[n["q_norm"]] = WeightSpec((self.nq * self.d if whole else self.d,), "gain")
             if not self.borrows:
                 specs[n["k_norm"]] = WeightSpec((self.nkv * self.d if whole else self.d,), "gain")
+        small = ("normal", 0.0, 0.02)
+        if self.bias:
+            specs[n["q_bias"]] = WeightSpec((self.nq * self.d,), "gain", small)
+            specs[n["o_bias"]] = WeightSpec((self.h,), "gain", small)
+            if not self.borrows:
+                specs[n["k_bias"]] = WeightSpec((self.nkv * self.d,), "gain", small)
+                specs[n["v_bias"]] = WeightSpec((self.nkv * self.dv,), "gain", small)
+        if self.score_bias == "log_distance":
+            specs[n["r1"]] = WeightSpec((self.nq,), "gain", ("uniform", 0.1, 1.0))
+            specs[n["r2"]] = WeightSpec((self.nq,), "gain", ("uniform", 0.05, 1.0))
+        if self.sink:
+            specs[n["sink"]] = WeightSpec((self.nq,), "gain", ("normal", 0.0, 1.0))
         return specs
 
     def bind(self, tensors):
@@ -94,7 +182,18 @@ class GQAttention(Mixer):
             w = torch.zeros((self.h, self.nq, self.pad), dtype=self.w_o.dtype, device=self.w_o.device)
             w[:, :, :self.dv] = self.w_o.view(self.h, self.nq, self.dv)
             self.w_o = w.view(self.h, self.nq * self.pad).contiguous()
-        self.slopes = self.position.score_slopes(self.nq)      # asked once: a step allocates nothing for it
+        # asked once: a step allocates nothing for it
+        self.extras = ScoreExtras(slopes=self.position.score_slopes(self.nq))
+        if self.score_bias == "log_distance":
+            if self.extras.slopes is not None:
+                raise ValueError("a position encoding with score slopes and a log_distance bias exclude each other")
+            self.extras = ScoreExtras(slopes=_f32(tensors[n["r1"]]), log_rates=_f32(tensors[n["r2"]]))
+        if self.sink:
+            self.extras.sinks = _f32(tensors[n["sink"]])
+        if self.bias:
+            parts = [tensors[n["q_bias"]]] if self.borrows else [tensors[n[k]] for k in ("q_bias", "k_bias", "v_bias")]
+            self.qkv_bias = _f32(torch.cat([p.reshape(-1) for p in parts]))
+            self.o_bias = _f32(tensors[n["o_bias"]])
         if self.qk_norm_eps is not None:
             self.q_gain = tensors[n["q_norm"]]
             self.k_gain = None if self.borrows else tensors[n["k_norm"]]
@@ -110,7 +209,7 @@ class GQAttention(Mixer):
         K.qkv_finish(qkv, q, cache.pages, self.q_gain, self.k_gain, cos, sin, ctx.positions, ctx.token_slot,
                      cache.block_table, self.nq, self.nkv, self.d, self.dv, self.pad, rot_dim,
                      self.qk_norm_eps or 0.0, self.scope == "projection", not self.borrows,
-                     bool(cache.writes) and not self.borrows, self.rt.err)
+                     bool(cache.writes) and not self.borrows, self.rt.err, bias=self.qkv_bias, q_temp=self.q_temp)
         return q
 
     def forward(self, x, ctx, cache, residual):
@@ -127,9 +226,6 @@ class GQAttention(Mixer):
         heads = (q, cache.pages, self.q_gain, self.k_gain, cos, sin, ctx.positions, ctx.token_slot,
                  cache.block_table, nq, nkv, d, rot_dim, self.qk_norm_eps or 0.0, cache.writes, self.rt.err)
         interleaved = bool(rot_dim and self.position.rotary_interleaved)
-        # a bias on the scores is known to the CUDA-core attention kernels only
-        slopes = self.slopes
-        tensor_core_attention = not self.exact and slopes is None
         # few tokens: the product finishes its heads itself (norm, rotation, cache write); else
         # the projection goes through memory and a second kernel does that
         fused = False
@@ -148,39 +244,11 @@ class GQAttention(Mixer):
         self._attend(q, ctx, cache, residual, t)
 
     def _attend(self, q, ctx, cache, residual, t):
-        nq, nkv, d = self.nq, self.nkv, self.pad
-        slopes = self.slopes
-        tensor_core_attention = not self.exact and slopes is None
-        attn = self.rt.rows(t, nq * d)
-        plan, done = None, False
-        if tensor_core_attention and d in (64, 128):
-            plan = ctx.attention_plan(self.window, K.attention_prefill_tc_tile_tokens())
-            done = not plan.n_tile or K.attention_prefill_tc(
-                q, cache.pages, attn, plan.tile_work, plan.n_tile, cache.block_table, nq, nkv, d,
-                self.window, self.scale, self.rt.err)
-        if not done:
-            plan = ctx.attention_plan(self.window)
-            if plan.n_tile:
-                K.attention_tile(q, cache.pages, attn, None, None, plan.tile_work, plan.n_tile,
-                                 cache.block_table, nq, nkv, d, self.window, self.scale, self.rt.err, slopes)
-        if plan.n_split:
-            part_acc = self.rt.rows(plan.n_slots, nq, d, dtype=torch.float32)
-            part_ml = self.rt.rows(plan.n_slots, nq, 2, dtype=torch.float32)
-            done = False
-            if tensor_core_attention:
-                done = K.attention_decode_mma(q, cache.pages, part_acc, part_ml, plan.split_work,
-                                              plan.n_split, cache.block_table, nq, nkv, d, self.window,
-                                              self.scale, self.rt.err)
-            if not done and not self.exact:
-                done = K.attention_decode(q, cache.pages, part_acc, part_ml, plan.split_work,
-                                          plan.n_split, cache.block_table, nq, nkv, d, self.window,
-                                          self.scale, self.rt.err, slopes)
-            if not done:
-                K.attention_tile(q, cache.pages, None, part_acc, part_ml, plan.split_work,
-                                 plan.n_split, cache.block_table, nq, nkv, d, self.window,
-                                 self.scale, self.rt.err, slopes)
-            K.attention_combine(part_acc, part_ml, attn, plan.combine_items, plan.n_combine, nq, d)
+        attn = attend(self.rt, q, ctx, cache, self.nq, self.nkv, self.pad, self.window, self.scale, self.exact,
+                      self.extras)
         K.gemm_nt(attn, self.w_o, residual, K.EPILOGUE_RESIDUAL, err=self.rt.err)
+        if self.o_bias is not None:
+            K.row_bias(residual, self.o_bias, add=True)
 
 
 @register_part("mixer", "gqa_attention")
@@ -188,4 +256,6 @@ def _build(spec, runtime, position=None, **_):
     return GQAttention(spec["hidden_size"], spec["num_heads"], spec["num_kv_heads"], spec["head_dim"],
                        spec["scale"], spec.get("window", 0), spec.get("qk_norm_eps"), position, runtime,
                        value_dim=spec.get("value_dim"), qk_norm_scope=spec.get("qk_norm_scope", "head"),
-                       borrows_kv=spec.get("borrows_kv", False), names=spec.get("names"))
+                       borrows_kv=spec.get("borrows_kv", False), names=spec.get("names"),
+                       bias=spec.get("bias", False), q_temp=spec.get("q_temp"), score_bias=spec.get("score_bias"),
+                       sink=spec.get("sink", False))

@@ -45,7 +45,9 @@ class CacheNeed:
     kind "paged_kv": keys and values of ``kv_heads`` x ``head_dim`` per token in
     pages; ``window`` > 0 means only the last ``window`` positions are read, so
     pages behind it can be given back.  kind "state": one tensor of
-    ``state_shape`` per request, of fixed size, in a slot.
+    ``state_shape`` per request, of fixed size, in a slot.  kind "several": the needs ``parts``
+    side by side (a mixer made of several, each with a cache of its own); the mixer gets a
+    ``LayerCache`` whose ``parts`` are theirs, in this order.
     """
 
     kind: str
@@ -54,6 +56,7 @@ class CacheNeed:
     window: int = 0
     state_shape: tuple[int, ...] = ()
     state_dtype: torch.dtype = torch.float32
+    parts: tuple = ()
 
     def widened(self, reader: "CacheNeed | None") -> "CacheNeed":
         """This need, kept for as long as ``reader`` (a layer that reads the entry without

@@ -32,6 +32,11 @@ class TokenEmbedding(Part):
         K.embed_gather(ids, self.table, h, self.rt.err)
         return h
 
+    def accumulate(self, h: torch.Tensor, ctx) -> None:
+        """h += what ``forward`` returned for this step: for a schedule that feeds the embedding
+        in again before a later run of a layer.  The table is read again; nothing is kept."""
+        K.embed_gather(ctx.token_ids, self.table, h, self.rt.err, accumulate=True)
+
 
 class LinearHead(Part):
     graph_safe = True

@@ -2,7 +2,8 @@
 (LockStep: engine/kernels/rmsnorm.py:30-38).  ``offset``: the stored tensor is the gain minus
 this number (a tensor that holds the gain minus one: offset 1); the sum is made once, in float32, when the
 weights arrive.  ``tensor``: the local name of the stored tensor ("weight"; "" where the norm's
-own prefix names it)."""
+own prefix names it).  ``groups`` > 1: the row is cut into that many equal consecutive parts and
+each is divided by its own root mean square (the gain still runs over the whole row)."""
 
 from __future__ import annotations
 
@@ -42,9 +43,12 @@ class NormedRows:
 class RMSNorm(Norm):
     graph_safe = True
 
-    def __init__(self, width: int, eps: float, runtime: Runtime, offset: float = 0.0, tensor: str = "weight"):
+    def __init__(self, width: int, eps: float, runtime: Runtime, offset: float = 0.0, tensor: str = "weight",
+                 groups: int = 1):
         self.width, self.eps, self.rt = int(width), float(eps), runtime
-        self.offset, self.tensor = float(offset), str(tensor)
+        self.offset, self.tensor, self.groups = float(offset), str(tensor), int(groups)
+        if self.groups < 1 or self.width % self.groups:
+            raise ValueError(f"a norm over {self.width} elements cannot be cut into {self.groups} equal parts")
         self.gain: torch.Tensor | None = None
 
     def weight_specs(self):
@@ -55,17 +59,22 @@ class RMSNorm(Norm):
         if self.offset:
             self.gain = (self.gain.to(torch.float32) + self.offset).contiguous()
 
-    def lazy(self, h, row_index=None) -> NormedRows:
-        """The rows of ``h`` to be normalised, for a part that sets ``accepts_normed_rows``."""
+    def lazy(self, h, row_index=None):
+        """The rows of ``h`` to be normalised, for a part that sets ``accepts_normed_rows`` (the
+        products that make the norm themselves know the norm over the whole row only: a norm in
+        groups hands over the finished tensor)."""
+        if self.groups > 1:
+            return self.forward(h, row_index)
         return NormedRows(self, h, row_index)
 
     def forward(self, h, row_index=None):
         rows = h.shape[0] if row_index is None else row_index.numel()
         out = self.rt.rows(rows, self.width)
-        K.rmsnorm(h, self.gain, out, self.eps, self.rt.err, row_index)
+        K.rmsnorm(h, self.gain, out, self.eps, self.rt.err, row_index, self.groups)
         return out
 
 
 @register_part("norm", "rmsnorm")
 def _build(spec, runtime, **_):
-    return RMSNorm(spec["width"], spec["eps"], runtime, spec.get("offset", 0.0), spec.get("tensor", "weight"))
+    return RMSNorm(spec["width"], spec["eps"], runtime, spec.get("offset", 0.0), spec.get("tensor", "weight"),
+                   spec.get("groups", 1))

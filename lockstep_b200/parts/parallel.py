@@ -1,0 +1,61 @@
+"""Mixers side by side: several mixers read the same normed rows, and the layer adds
+sum_b scale_b * mixer_b(x) to the residual stream.
+
+``branches``: a list of {"name": tensor-name prefix under the mixer's own, "mixer": PartSpec,
+"position": PartSpec or None, "scale": number}.  Each branch keeps a cache of its own (pages or
+a state slot): the part's need is the branches' needs side by side.  A branch adds its result
+into a float32 buffer of its own as it would into the residual stream (so any registered mixer
+can be a branch); one kernel then adds the weighted buffers to the residual stream.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import kernels as K
+from ..config.spec import PartSpec, own_tensors, tensor_name
+from .base import CacheNeed, Mixer, Runtime, build_part, register_part
+
+
+class ParallelMixers(Mixer):
+    def __init__(self, hidden_size, branches, runtime: Runtime):
+        if not 1 <= len(branches) <= 4:
+            raise ValueError("one to four mixers can run side by side")
+        self.w, self.rt = int(hidden_size), runtime
+        self.names, self.scales, self.mixers = [], [], []
+        for b in branches:
+            position = build_part("position", b.get("position") or PartSpec("none"), runtime)
+            self.names.append(str(b["name"]))
+            self.scales.append(float(b.get("scale", 1.0)))
+            self.mixers.append(build_part("mixer", b["mixer"], runtime, position=position))
+
+    @property
+    def graph_safe(self):
+        return all(m.graph_safe for m in self.mixers)
+
+    def cache_need(self):
+        return CacheNeed("several", parts=tuple(m.cache_need() for m in self.mixers))
+
+    def attention_windows(self):
+        return set().union(*(m.attention_windows() for m in self.mixers))
+
+    def weight_specs(self):
+        return {tensor_name(name, local): spec for name, m in zip(self.names, self.mixers)
+                for local, spec in m.weight_specs().items()}
+
+    def bind(self, tensors):
+        for name, m in zip(self.names, self.mixers):
+            m.bind(own_tensors(name, tensors))
+
+    def forward(self, x, ctx, cache, residual):
+        n, t = len(self.mixers), residual.shape[0]
+        out = self.rt.rows(n * t, self.w, dtype=torch.float32).view(n, t, self.w)
+        K.row_bias(out.view(n * t, self.w), None)
+        for i, m in enumerate(self.mixers):
+            m.forward(x, ctx, cache.parts[i], out[i])
+        K.weighted_sum(residual, out, self.scales)
+
+
+@register_part("mixer", "parallel")
+def _build(spec, runtime, **_):
+    return ParallelMixers(spec["hidden_size"], spec["branches"], runtime)

@@ -17,6 +17,12 @@ output projection.  The slot also carries what the next portion needs of the tok
   one before it (carried across portions): x + (x_prev - x) mu;  w = exp(-exp(W_w2 tanh(W_w1 m) +
   w0)); the read-out is normed per head, times a gain over all heads, times silu(W_g m).
 
+"gated_linear" (per head, with a decay a per key channel):
+    S <- diag(a_t) S + k_t v_t^T;  o_t = S^T q_t
+  q = W_q x * dk^(-1/2), k, v straight from their projections; a = sigmoid(W_a2 W_a1 x + b)^(1/tau),
+  made through its logarithm; the read-out is normed per head, times a gain shared by the heads,
+  times silu(W_g x).  Nothing but S is carried.
+
 The projections run as the engine's products (tensor cores in bfloat16); everything between
 them and the recurrence, the recurrence and the state are float32 (csrc/recurrent.cu).
 """
@@ -185,6 +191,72 @@ class Wkv(Mixer):
         y = rt.rows(tokens, self.A)
         K.head_rms_gate(o, self.gain, None, g, y, self.H, self.d, False, self.eps)
         K.gemm_nt(y, self.w_o, residual, K.EPILOGUE_RESIDUAL, err=rt.err)
+
+
+class GatedLinear(Mixer):
+    graph_safe = True
+    accepts_normed_rows = True
+
+    def __init__(self, hidden_size, num_heads, key_dim, value_dim, tau, norm_eps, runtime: Runtime, decay_rank=None):
+        if key_dim > 256:
+            raise ValueError(f"key_dim {key_dim} is not supported (up to 256)")
+        if not float(tau) > 0:
+            raise ValueError("tau must be positive")
+        self.w, self.H, self.dk, self.dv = int(hidden_size), int(num_heads), int(key_dim), int(value_dim)
+        self.tau, self.eps, self.rt = float(tau), float(norm_eps), runtime
+        self.Kd, self.Vd = self.H * self.dk, self.H * self.dv
+        self.rank = int(decay_rank or -1)      # -1: whatever the stored tensors have
+
+    def cache_need(self):
+        return CacheNeed("state", state_shape=(self.H * self.dk * self.dv,), state_dtype=torch.float32)
+
+    def weight_specs(self):
+        return {"q": WeightSpec((self.Kd, self.w)), "k": WeightSpec((self.Kd, self.w)), "v": WeightSpec((self.Vd, self.w)),
+                "g": WeightSpec((self.Vd, self.w)), "o": WeightSpec((self.w, self.Vd)),
+                "norm": WeightSpec((self.dv,), "gain"),
+                "a1": WeightSpec((self.rank, self.w)), "a2": WeightSpec((self.Kd, self.rank)),
+                "a2.b": WeightSpec((self.Kd,), "gain", ("normal", 3.0, 1.0))}
+
+    def bind(self, t):
+        if t["a1"].shape[0] != t["a2"].shape[1]:
+            raise ValueError("the two halves of the decay's low-rank map do not have the same rank")
+        # one product for everything that reads the mixer's input; every part starts at a column
+        # that is a multiple of 8, so that kernels and products can take it where it lies
+        zeros = lambda rows: torch.zeros((rows, self.w), dtype=t["q"].dtype, device=t["q"].device)
+        parts, self.at, col = [], {}, 0
+        for name in ("q", "k", "v", "g", "a1"):
+            self.at[name] = col
+            parts += [t[name], zeros(-t[name].shape[0] % 8)]
+            col += t[name].shape[0] + (-t[name].shape[0] % 8)
+        self.ra = t["a1"].shape[0]
+        self.w_in = torch.cat(parts, dim=0).contiguous()
+        self.w_a2, self.w_o = t["a2"].contiguous(), t["o"]
+        self.a_bias, self.gain = _f32(t["a2.b"]), _f32(t["norm"])
+
+    def forward(self, x, ctx, cache, residual):
+        rt, tokens, at = self.rt, residual.shape[0], self.at
+        proj = rt.rows(tokens, self.w_in.shape[0])
+        if isinstance(x, NormedRows):
+            x.linear(self.w_in, proj, K.EPILOGUE_STORE, rt.err)
+        else:
+            K.gemm_nt(x, self.w_in, proj, err=rt.err)
+        decay = rt.rows(tokens, self.Kd, dtype=torch.float32)
+        K.gemm_nt(proj[:, at["a1"]:at["a1"] + self.ra], self.w_a2, decay, err=rt.err)
+        K.sigmoid_power_decay(decay, self.a_bias, self.tau)
+        portions, cap = portion_list(ctx, cache.state, rt)
+        o = rt.rows(tokens, self.Vd, dtype=torch.float32)
+        K.state_rule(K.RULE_GLA, rt.dtype, portions, cap, cache.state, proj[:, at["q"]:at["q"] + self.Kd],
+                     proj[:, at["k"]:at["k"] + self.Kd], proj[:, at["v"]:at["v"] + self.Vd], decay, None, None, o,
+                     None, 0, 0, self.H, self.H, self.dk, self.dv, out_scale=self.dk ** -0.5)
+        y = rt.rows(tokens, self.Vd)
+        K.head_rms_gate(o, self.gain, None, proj[:, at["g"]:at["g"] + self.Vd], y, self.H, self.dv, True, self.eps)
+        K.gemm_nt(y, self.w_o, residual, K.EPILOGUE_RESIDUAL, err=rt.err)
+
+
+@register_part("mixer", "gated_linear")
+def _build_gated_linear(spec, runtime, **_):
+    return GatedLinear(spec["hidden_size"], spec["num_heads"], spec["key_dim"], spec["value_dim"], spec["tau"],
+                       spec["norm_eps"], runtime, decay_rank=spec.get("decay_rank"))
 
 
 @register_part("mixer", "gated_delta")
