@@ -378,7 +378,8 @@ def _rows(t: torch.Tensor, name: str) -> tuple[int, int]:
         raise KernelError(f"{name} must live on a CUDA device; there is no CPU fallback")
     if t.dim() != 2 or t.stride(1) != 1 or (t.shape[0] > 1 and t.stride(0) < t.shape[1]):
         raise KernelError(f"{name} must be two-dimensional with contiguous rows")
-    return t.data_ptr(), (t.stride(0) if t.shape[0] > 1 else t.shape[1])
+    # (a single row's stride says nothing about the rows; a view of a wider row keeps its pitch)
+    return t.data_ptr(), (t.stride(0) if t.stride(0) >= t.shape[1] else t.shape[1])
 
 
 def gemm_nt_simt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPILOGUE_STORE) -> None:
