@@ -33,7 +33,7 @@ def query_temperature(n, coef, every, dtype=torch.float64):
     return 1.0 + coef * torch.log((torch.div(p + 1, every, rounding_mode="floor") + 1).to(dtype))
 
 
-def log_distance_attention(q, k, v, scale, r1, r2):
+def log_distance_attention(q, k, v, scale, r1, r2, weights=False):
     """q [n, H, d], k [n, G, d], v [n, G, dv], r1 and r2 [H].  Causal softmax attention whose
     score for query i and key j <= i is q.k scale - r1 ln(1 + r2 (i - j))."""
     n, H, _ = q.shape
@@ -45,10 +45,12 @@ def log_distance_attention(q, k, v, scale, r1, r2):
     dist = (i - j).clamp(min=0).to(q.dtype)
     scores = scores - r1[:, None, None] * torch.log1p(r2[:, None, None] * dist[None])
     scores = scores.masked_fill((j > i)[None], float("-inf"))
+    if weights:
+        return torch.softmax(scores, dim=-1)
     return torch.einsum("hij,jhd->ihd", torch.softmax(scores, dim=-1), vv)
 
 
-def biased_attention_mixer(x, w, p, m):
+def biased_attention_mixer(x, w, p, m, weights=False):
     n = x.shape[0]
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     q = (x @ w[p + ".q"].T + w[p + ".q.b"]).view(n, H, d)
@@ -57,7 +59,9 @@ def biased_attention_mixer(x, w, p, m):
     t = m.get("q_temp")
     if t:
         q = q * query_temperature(n, t["coef"], t["every"], x.dtype)[:, None, None]
-    o = log_distance_attention(q, k, v, m["scale"], w[p + ".r1"], w[p + ".r2"])
+    o = log_distance_attention(q, k, v, m["scale"], w[p + ".r1"], w[p + ".r2"], weights)
+    if weights:
+        return o
     return o.reshape(n, H * dv) @ w[p + ".o"].T + w[p + ".o.b"]
 
 
@@ -131,10 +135,11 @@ def rotate_pairs(x, cos, sin):
     return torch.stack([u * c - v * s, v * c + u * s], dim=-1).flatten(-2)
 
 
-def sink_window_attention(q, k, v, scale, window, sink):
+def sink_window_attention(q, k, v, scale, window, sink, weights=False):
     """q [n, H, d], k [n, H, d], v [n, H, dv], sink [H].  Query i sees keys j with
     0 <= i - j < window (all j <= i for window 0); the softmax's denominator also holds
-    exp(sink) of the head, which has no value."""
+    exp(sink) of the head, which has no value.  ``weights``: return the softmax's weights
+    [H, n, n] instead."""
     n = q.shape[0]
     scores = torch.einsum("ihd,jhd->hij", q, k) * scale
     i = torch.arange(n)[:, None]
@@ -144,10 +149,12 @@ def sink_window_attention(q, k, v, scale, window, sink):
     top = torch.maximum(scores.max(-1, keepdim=True).values, sink[:, None, None])
     e = torch.exp(scores - top)
     p = e / (e.sum(-1, keepdim=True) + torch.exp(sink[:, None, None] - top))
+    if weights:
+        return p
     return torch.einsum("hij,jhd->ihd", p, v)
 
 
-def latent_attention_mixer(x, w, p, m, eps):
+def latent_attention_mixer(x, w, p, m, eps, weights=False):
     n = x.shape[0]
     H, d, dr, dv, rank = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
     rot = m["rot"]
@@ -161,7 +168,9 @@ def latent_attention_mixer(x, w, p, m, eps):
     k_plain = (c @ w[p + ".uk"].T).view(n, H, d)
     v = (c @ w[p + ".uv"].T).view(n, H, dv)
     o = sink_window_attention(torch.cat([q_plain, q_rot], -1), torch.cat([k_plain, k_rot], -1), v,
-                              m["scale"], (m.get("mask") or {}).get("size", 0), w[p + ".sink"])
+                              m["scale"], (m.get("mask") or {}).get("size", 0), w[p + ".sink"], weights)
+    if weights:
+        return o
     return o.reshape(n, H * dv) @ w[p + ".o"].T
 
 
@@ -219,3 +228,21 @@ def forward(cfg, w, tokens, dtype=torch.float64, trace=None):
             trace.append(x.clone())
     x = grouped_rms_norm(x, w["final.norm"], cfg["norm"]["eps"], cfg["norm"].get("groups", 1))
     return x @ w["embed"].T
+
+
+def read_model_folder(folder):
+    """(config dictionary, tensors by name in float64) of a model folder."""
+    import json
+    from pathlib import Path
+
+    from safetensors.torch import load_file
+
+    folder = Path(folder)
+    cfg = json.loads((folder / "config.json").read_text())
+    w = {k: (v.double() if v.is_floating_point() else v) for k, v in load_file(str(folder / "model.safetensors")).items()}
+    return cfg, w
+
+
+def model_logits(folder, tokens, dtype=torch.float64):
+    cfg, w = read_model_folder(folder)
+    return forward(cfg, w, tokens, dtype)
