@@ -33,6 +33,10 @@ to 2,048 tokens and 128 decoded tokens each through the entry point.
 Sevipel design (windowed attention, gated delta rule, wkv rule, routed experts) at two sizes
 beside Qwen3 layers of equal width, depth and active feed-forward weights, and every kernel
 of an unrecorded step of each with its fraction of the measured peaks.
+``--workload malazen`` does the same for the Malazen design (softmax attention with a distance
+bias beside gated linear attention, attention over a cached latent, a clamped gated feed-forward,
+two of the layers run twice) beside Qwen3 layers of equal width, depth, head counts and
+feed-forward size.
 """
 
 from __future__ import annotations
@@ -564,7 +568,8 @@ def kernel_times(runner, entries_of, steps=3):
              "gemm_nt_tc_qkv_heads", "attention_tile", "attention_decode", "attention_decode_mma",
              "attention_prefill_tc", "attention_combine", "qkv_finish", "find_portions", "delta_prep", "shift_mix",
              "tanh_rows", "double_exp_decay", "state_rule", "head_rms_gate", "experts_route", "experts_plan", "experts_product",
-             "experts_product_tc", "experts_gather", "experts_combine"]
+             "experts_product_tc", "experts_gather", "experts_combine", "latent_finish", "heads_product",
+             "sigmoid_power_decay", "clamped_glu", "row_bias", "weighted_sum"]
     records, saved, graphs = [], {}, runner.graphs
     runner.graphs = None
 
@@ -572,7 +577,7 @@ def kernel_times(runner, entries_of, steps=3):
         def timed(*a, **kw):
             label = name
             if name == "state_rule":
-                label = "delta_rule" if a[0] == K.RULE_DELTA else "wkv_rule"
+                label = {K.RULE_DELTA: "delta_rule", K.RULE_WKV: "wkv_rule", K.RULE_GLA: "gla_rule"}[a[0]]
             elif name in ("experts_product", "experts_product_tc"):
                 label = "experts_up" if a[0] == 0 else "experts_down"
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -682,6 +687,132 @@ def run_designs(args):
         "metric": "prefill of 2,048 tokens and decode at batch 8, context 2,048: Sevipel beside Qwen3 layers of equal size",
         "unit": "ms, tok/s", "n_gpus": 1, "dtype": "bf16", "data": "synthetic", "impl": "ours", "clocks": clock,
         "peaks": pk, "layers": DESIGN_LAYERS, "vocab": DESIGN_VOCAB, "sizes": sizes,
+    }))
+    return 0
+
+
+MALAZEN_SIZES = {
+    "w1024": {"width": 1024, "heads": 8, "kv_heads": 4, "linear_heads": 4, "latent_heads": 8, "ff": 3072},
+    "w2048": {"width": 2048, "heads": 16, "kv_heads": 4, "linear_heads": 8, "latent_heads": 16, "ff": 6144},
+}
+MALAZEN_RANK, MALAZEN_ROT, MALAZEN_PLAIN, MALAZEN_VALUE, MALAZEN_WINDOW = 192, 64, 64, 128, 1024
+
+
+def malazen_configs(z):
+    """(Malazen configuration, Qwen3 configuration) of one size: eight layer runs (six layers, two of
+    them run twice), the same width, query and key heads, head size and feed-forward size."""
+    mlp = {"kind": "dense", "ff": z["ff"], "limit": 7.0}
+    par = {"left": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                    "q_temp": {"coef": 0.1, "every": 1024}},
+           "right": {"heads": z["linear_heads"], "dim": 128, "vdim": 128, "tau": 16.0, "decay_rank": 64},
+           "left_scale": 0.8, "right_scale": 0.9}
+    lat = {"heads": z["latent_heads"], "dim": MALAZEN_PLAIN, "rot_dim": MALAZEN_ROT, "vdim": MALAZEN_VALUE,
+           "kv_rank": MALAZEN_RANK, "scale": (MALAZEN_PLAIN + MALAZEN_ROT) ** -0.5, "mask": {"size": MALAZEN_WINDOW},
+           "rot": {"dims": MALAZEN_ROT, "base": 1000000.0,
+                   "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}}}
+    kinds = [("parallel", par), ("latent_attention", lat), ("latent_attention", lat), ("parallel", par),
+             ("parallel", par), ("latent_attention", lat)]
+    malazen = {"architecture": "Malazen", "vocab": DESIGN_VOCAB, "width": z["width"], "norm": {"eps": 1e-5, "groups": 2},
+               "max_positions": 4096, "loop": {"start": 1, "stop": 3, "times": 2},
+               "layers": [{"type": t, "mixer": json.loads(json.dumps(m)), "mlp": mlp} for t, m in kinds]}
+    qwen = dict(QWEN3_0_6B, num_hidden_layers=DESIGN_LAYERS, hidden_size=z["width"], num_attention_heads=z["heads"],
+                num_key_value_heads=z["kv_heads"], head_dim=128, vocab_size=DESIGN_VOCAB,
+                intermediate_size=z["ff"], max_position_embeddings=4096)
+    return malazen, qwen
+
+
+def run_malazen(args):
+    import torch
+
+    from lockstep_b200 import StepEntry
+
+    pk = peaks()
+    tokens, batch, context = PREFILL_TOKENS, 8, DESIGN_CONTEXT
+    sizes = {}
+    clocks = ClockSampler()
+    clocks.start()
+    for size, z in MALAZEN_SIZES.items():
+        malazen, qwen = malazen_configs(z)
+        row = {}
+        for design, cfg in (("malazen", malazen), ("qwen3", qwen)):
+            engine = build_engine(cfg, "bfloat16", batch, context + 64)
+            runner = engine.runner
+            prefill = time_prefill(runner, tokens)
+            decode = time_decode(runner, engine.sampler, batch, context, 100, args.warmup, repeats=3)
+            ids = [(5 * i + 3) % 1000 for i in range(tokens)]
+
+            def prefill_step(r):
+                runner.open(f"k{r}")
+                runner.step([StepEntry(uid=f"k{r}", tokens=ids, start=0, want=[tokens - 1])], check=False)
+                return lambda: runner.close(f"k{r}")
+
+            def decode_step(r):
+                uids = [f"q{r}_{i}" for i in range(batch)]
+                for u in uids:
+                    runner.open(u)
+                    runner.fill_random(u, context - 1)
+                runner.step([StepEntry(uid=u, tokens=[7], start=context - 1, want=[0]) for u in uids], check=False)
+                return lambda: [runner.close(u) for u in uids]
+
+            p_kernels, p_launches = kernel_times(runner, prefill_step)
+            d_kernels, d_launches = kernel_times(runner, decode_step)
+            p_ms, d_ms = statistics.median(prefill), statistics.median(decode)
+            row[design] = {
+                "prefill_ms": round(p_ms, 3), "prefill_tok_s": round(tokens / p_ms * 1e3, 1),
+                "decode_ms_per_step": round(d_ms, 4), "decode_tok_s": round(batch / d_ms * 1e3, 1),
+                "prefill_kernels_ms": p_kernels, "prefill_launches": p_launches,
+                "decode_kernels_ms": d_kernels, "decode_launches": d_launches,
+            }
+            del engine, runner
+            torch.cuda.empty_cache()
+        m, q = row["malazen"], row["qwen3"]
+        w, ff, H, G, LH, QH = z["width"], z["ff"], z["heads"], z["kv_heads"], z["linear_heads"], z["latent_heads"]
+        runs_par, runs_lat = 3, 5
+        D = -(-(MALAZEN_RANK + MALAZEN_ROT) // 16) * 16
+        # products of a prefill (the engine's product kernels; the per-head products are listed apart)
+        par_cols = (H + 2 * G) * 128 + H * 128 + (2 * LH * 128 + 2 * LH * 128 + 64) + LH * 128
+        lat_cols = QH * (MALAZEN_PLAIN + MALAZEN_ROT) + MALAZEN_RANK + MALAZEN_ROT + QH * MALAZEN_VALUE
+        flops_m = 2 * tokens * (runs_par * par_cols * w + runs_lat * lat_cols * w + 8 * 3 * ff * w) + 2 * DESIGN_VOCAB * w
+        flops_q = 2 * tokens * 8 * ((H + 2 * G) * 128 * w + H * 128 * w + 3 * ff * w) + 2 * DESIGN_VOCAB * w
+        # attention of a prefill: scores and weighted values over the causal half (windowed for the latent layers)
+        pairs_full = tokens * (tokens + 1) // 2
+        pairs_win = sum(min(i + 1, MALAZEN_WINDOW) for i in range(tokens))
+        att_m = runs_par * 4 * pairs_full * H * 128 + runs_lat * 4 * pairs_win * QH * D
+        att_q = 8 * 4 * pairs_full * H * 128
+        heads_flops = runs_lat * 2 * tokens * QH * MALAZEN_RANK * (MALAZEN_PLAIN + MALAZEN_VALUE)
+        # bytes a decode step's attention reads, and the linear side's state read and written
+        cache_m = 2 * batch * (runs_par * context * 2 * G * 128 + runs_lat * min(context, MALAZEN_WINDOW) * 2 * D)
+        cache_q = 2 * batch * 8 * context * 2 * G * 128
+        state_m = 2 * 4 * batch * runs_par * LH * 128 * 128
+
+        def frac(amount, ms, peak):
+            return round(amount / (ms * 1e-3) / peak, 4) if ms else None
+
+        def ms_of(kernels, *names):
+            return sum(kernels.get(n, 0.0) for n in names)
+
+        tf, bw = pk["bf16_tflops"] * 1e12, pk["hbm_gbs"] * 1e9
+        row["like_kernels_fraction_of_measured_peak [malazen, qwen3]"] = {
+            "prefill: products (tensor cores)": [
+                frac(flops_m, ms_of(m["prefill_kernels_ms"], "gemm_nt_tc", "gemm_nt_tc_rmsnorm"), tf),
+                frac(flops_q, ms_of(q["prefill_kernels_ms"], "gemm_nt_tc", "gemm_nt_tc_rmsnorm"), tf)],
+            "prefill: attention": [
+                frac(att_m, ms_of(m["prefill_kernels_ms"], "attention_tile", "attention_prefill_tc"), tf),
+                frac(att_q, ms_of(q["prefill_kernels_ms"], "attention_tile", "attention_prefill_tc"), tf)],
+            "prefill: per-head products of the latent layers (no like kernel)": [
+                frac(heads_flops, ms_of(m["prefill_kernels_ms"], "heads_product"), tf), None],
+            "decode: attention (bytes of cache)": [
+                frac(cache_m, ms_of(m["decode_kernels_ms"], "attention_decode", "attention_decode_mma", "attention_tile"), bw),
+                frac(cache_q, ms_of(q["decode_kernels_ms"], "attention_decode", "attention_decode_mma", "attention_tile"), bw)],
+            "decode: linear side's rule (bytes of state; no like kernel)": [
+                frac(state_m, ms_of(m["decode_kernels_ms"], "gla_rule"), bw), None],
+        }
+        sizes[size] = row
+    clock = clocks.stop()
+    print(json.dumps({
+        "metric": "prefill of 2,048 tokens and decode at batch 8, context 2,048: Malazen beside Qwen3 layers of equal size",
+        "unit": "ms, tok/s", "n_gpus": 1, "dtype": "bf16", "data": "synthetic", "impl": "ours", "clocks": clock,
+        "peaks": pk, "layer_runs": 8, "vocab": DESIGN_VOCAB, "sizes": sizes,
     }))
     return 0
 
@@ -855,7 +986,7 @@ def main():
     ap.add_argument("--no-fp32", action="store_true", help="skip the float32 points")
     ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
                     help="time only this part and print a short line (for profiling a small case)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "mixed", "designs"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "mixed", "designs", "malazen"],
                     help="mixed: a continuous batch of 64 requests through the entry point; designs: the Sevipel "
                          "design beside Qwen3 layers of equal size, with every kernel's time")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"],
@@ -875,6 +1006,8 @@ def main():
         return run_mixed(args)
     if args.workload == "designs":
         return run_designs(args)
+    if args.workload == "malazen":
+        return run_malazen(args)
     return run_ours(args)
 
 
