@@ -50,7 +50,8 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap map, const __nv_
                             float* __restrict__ part_acc, float* __restrict__ part_ml,
                             const int* __restrict__ work, const int* __restrict__ block_table,
                             int table_stride, int nq, int nkv, int page_size, int num_pages, int window,
-                            float scale, int* err) {
+                            float scale, const float* __restrict__ slopes, const float* __restrict__ log_rates,
+                            int* err) {
   // The work list, the block table and every key older than this step's token are there
   // before the step's first kernel starts, so the first chunks are fetched while the kernel
   // before this one (which writes the token's own key and value, and q) still runs.
@@ -92,6 +93,16 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap map, const __nv_
   __syncwarp();
 
   const int r0 = lane >> 2, cq = (lane & 3) * 2;   // this thread holds rows r0 and r0 + 8
+  // a bias that grows with the logarithm of the distance, per query head (rows past the group: none)
+  float bias_a[2] = {0.f, 0.f}, bias_b[2] = {0.f, 0.f};
+  if (log_rates != nullptr) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+      if (r0 + 8 * r < nq / nkv) {
+        bias_a[r] = slopes[(int)blockIdx.y * (nq / nkv) + r0 + 8 * r];
+        bias_b[r] = log_rates[(int)blockIdx.y * (nq / nkv) + r0 + 8 * r];
+      }
+  }
 
   float acc[DTILES][4];
 #pragma unroll
@@ -222,7 +233,10 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap map, const __nv_
       for (int e = 0; e < 4; ++e) {
         const int key = c0 + nt * 8 + cq + (e & 1);
         const bool keep = key < s_hi && key >= row_lo;
-        s[nt][e] = keep ? s[nt][e] * scale : -CUDART_INF_F;
+        // (log_rates: slopes[head] x ln(1 + log_rates[head] x distance) is taken off the score)
+        s[nt][e] = !keep ? -CUDART_INF_F
+                   : log_rates != nullptr ? s[nt][e] * scale - bias_a[e >> 1] * log1pf(bias_b[e >> 1] * (float)(pos - key))
+                                          : s[nt][e] * scale;
         tile_max[e >> 1] = fmaxf(tile_max[e >> 1], s[nt][e]);
       }
     float alpha[2];
@@ -369,7 +383,8 @@ EncodeTiled encode_fn() {
 template <int HALVES>
 int launch(const CUtensorMap& map, const void* q, float* part_acc, float* part_ml, const int* work,
            int n_work, const int* block_table, int table_stride, int nq, int nkv, int page_size,
-           int num_pages, int window, float scale, int* err, cudaStream_t stream) {
+           int num_pages, int window, float scale, const float* slopes, const float* log_rates, int* err,
+           cudaStream_t stream) {
   const size_t smem = (size_t)WARPS * 2 * HALVES * CHUNK * 128 + 128 + 16 * HALVES * 128 + 1024;
   static bool configured = false;
   if (!configured) {
@@ -381,7 +396,7 @@ int launch(const CUtensorMap& map, const void* q, float* part_acc, float* part_m
   dim3 grid(n_work, nkv);
   LS_COUNT(LS_K_ATTENTION_DECODE_MMA), ls_launch(attention_decode_mma_kernel<HALVES>, grid, WARPS * 32, smem, stream, 
       map, (const __nv_bfloat16*)q, part_acc, part_ml, work, block_table, table_stride, nq, nkv, page_size,
-      num_pages, window, scale, err);
+      num_pages, window, scale, slopes, log_rates, err);
   return ls_launch_status();
 }
 
@@ -392,9 +407,10 @@ int launch(const CUtensorMap& map, const void* q, float* part_acc, float* part_m
 LS_API int ls_attention_decode_mma(const void* q, const void* pages, float* part_acc, float* part_ml,
                                    const int* work, int n_work, const int* block_table,
                                    int table_stride, int nq, int nkv, int d, int page_size,
-                                   int num_pages, int window, float scale, int* err,
-                                   cudaStream_t stream) {
+                                   int num_pages, int window, float scale, const float* slopes,
+                                   const float* log_rates, int* err, cudaStream_t stream) {
   if (n_work <= 0) return 0;
+  if ((slopes != nullptr) != (log_rates != nullptr)) return LS_E_SIZE;      // a linear bias alone: the CUDA-core kernels
   if (nq <= 0 || nkv <= 0 || nq % nkv || nq / nkv > 16 || nkv > 65535) return LS_E_SIZE;
   if (d != 64 && d != 128) return LS_E_SIZE;
   if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64) return LS_E_SIZE;
@@ -413,9 +429,9 @@ LS_API int ls_attention_decode_mma(const void* q, const void* pages, float* part
     return LS_E_SIZE;
   if (d == 64)
     return launch<1>(map, q, part_acc, part_ml, work, n_work, block_table, table_stride, nq, nkv, page_size,
-                     num_pages, window, scale, err, stream);
+                     num_pages, window, scale, slopes, log_rates, err, stream);
   return launch<2>(map, q, part_acc, part_ml, work, n_work, block_table, table_stride, nq, nkv, page_size,
-                   num_pages, window, scale, err, stream);
+                   num_pages, window, scale, slopes, log_rates, err, stream);
 }
 
 LS_API const char* ls_constants_attention_decode_mma() {

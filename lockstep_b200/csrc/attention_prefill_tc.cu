@@ -109,6 +109,13 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// lg2 x on the special-function unit, one instruction (inputs here are >= 1)
+__device__ __forceinline__ float lg2(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // Two float32 lanes an instruction (sm_100: fma / add on pairs of registers) and the maximum of
 // three: the softmax warps are short of issue slots, and each of these halves an instruction
 // count without changing a result (every lane is rounded as the single instruction rounds it).
@@ -151,12 +158,17 @@ struct Item {
 // buffers count on over the items of a block (tile counter `gt`), the producers run ahead into
 // the next item's Q and first tiles while the softmax of the last tile still runs, and the
 // tensor memory is allocated once: an item after the first does not pay a block's start again.
-template <int HALVES>
+// EXTRAS: the scores may get a bias that grows with the logarithm of the distance of key and query taken
+// off (slopes[head] x ln(1 + log_rates[head] x distance): in the units of the exponentials,
+// slopes[head] x lg2(1 + log_rates[head] x distance), one more special-function instruction a score),
+// and the softmax's denominator one more term exp(sinks[head]) at the end of a row.
+template <int HALVES, bool EXTRAS>
 __global__ void __launch_bounds__(THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                             __nv_bfloat16* __restrict__ out, const int* __restrict__ work, int n_work,
                             const int* __restrict__ block_table, int table_stride, int nq, int nkv, int page_size,
-                            int num_pages, int window, float scale_log2, int* err) {
+                            int num_pages, int window, float scale_log2, const float* __restrict__ slopes,
+                            const float* __restrict__ log_rates, const float* __restrict__ sinks, int* err) {
   ls_dependency_trigger();
   constexpr int D = HALVES * 64;
   constexpr int KV_BYTES = HALVES * HALF_BYTES;          // K (or V) of one tile; also Q
@@ -413,6 +425,17 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
       const int lo_last = (window > 0 && pos_last - window + 1 > 0) ? pos_last - window + 1 : 0;
       float m_ref = -CUDART_INF_F, l_run = 0.f;
+      float bias_a = 0.f, bias_b = 0.f;
+      bool biased = false;
+      if constexpr (EXTRAS) {
+        if (log_rates != nullptr) {
+          bias_a = slopes[I.h];
+          bias_b = log_rates[I.h];
+          biased = true;
+        }
+      }
+      // with a bias the scores are put into the exponentials' units as they are read, and no scale is left
+      const float scale_eff = biased ? 1.0f : scale_log2;
       for (int it = 0; it < n_tiles; ++it) {
         const int g = gt + it;
         const int s = g & 1;
@@ -424,6 +447,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
         for (int q0 = 0; q0 < HC; q0 += 32) tmem_ld32(lane_base + S_COL + s * BLOCK_N + group * HC + q0, sc + q0);
         tmem_ld_wait();
+        if constexpr (EXTRAS) {
+          if (biased) {
+            const float d0 = (float)(pos - c0);        // distance of this thread's first key (masked keys: clamped)
+#pragma unroll
+            for (int jj = 0; jj < HC; ++jj) {
+              const float dist = fmaxf(d0 - (float)jj, 0.f);
+              sc[jj] = __float_as_uint(fmaf(__uint_as_float(sc[jj]), scale_log2, -bias_a * lg2(fmaf(bias_b, dist, 1.0f))));
+            }
+          }
+        }
         // every key of the tile is seen by every row: no masks (uniform over the block)
         const bool full_tile = (tile_first + it) * BLOCK_N + BLOCK_N - 1 <= pos0 && (tile_first + it) * BLOCK_N >= lo_last;
         float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
@@ -446,7 +479,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
         for (int o = 0; o < GROUPS; ++o) tile_max = fmaxf(tile_max, row_max[(it & 1) * ROWS + o * 128 + row]);
         // all threads of a row work out the same m_ref from the same numbers
-        const float m_new = tile_max * scale_log2;
+        const float m_new = tile_max * scale_eff;
         const bool move = m_new > m_ref + LAZY;                      // true too for the first key a row sees
         const float factor = move ? ((m_ref == -CUDART_INF_F) ? 0.f : ex2(m_ref - m_new)) : 1.f;
         if (move) m_ref = m_new;
@@ -482,7 +515,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
               for (int jj = 0; jj < 8; jj += 2) {
                 p[jj] = __uint_as_float(sc[n0 + jj]);
                 p[jj + 1] = __uint_as_float(sc[n0 + jj + 1]);
-                fma2(p[jj], p[jj + 1], scale_log2, neg_m);
+                fma2(p[jj], p[jj + 1], scale_eff, neg_m);
                 p[jj] = ex2(p[jj]);
                 p[jj + 1] = ex2(p[jj + 1]);
               }
@@ -492,7 +525,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
               for (int jj = 0; jj < 8; ++jj) {
                 const int key = c0 + n0 + jj;
                 const bool keep = (key <= pos) & (key >= lo) & !dead;
-                p[jj] = ex2(keep ? fmaf(__uint_as_float(sc[n0 + jj]), scale_log2, neg_m) : -CUDART_INF_F);
+                p[jj] = ex2(keep ? fmaf(__uint_as_float(sc[n0 + jj]), scale_eff, neg_m) : -CUDART_INF_F);
               }
             }
             add2(ps[0], ps[1], p[0], p[1]);
@@ -530,6 +563,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       float l_row = l_part[row];                     // the same sum in the same order in each of the row's threads
 #pragma unroll
       for (int o = 1; o < GROUPS; ++o) l_row += l_part[o * 128 + row];
+      if constexpr (EXTRAS) {
+        // the sink, in the units of this row's sums (2^m_ref): every thread of the row adds the same
+        if (sinks != nullptr && m_ref != -CUDART_INF_F) l_row += ex2(fmaf(sinks[I.h], 1.4426950408889634f, -m_ref));
+      }
       const int g_last = gt + n_tiles - 1;
       if (ok && !mbar_wait(&o_full[g_last & 1], (uint32_t)(g_last >> 1) & 1u)) ok = false;
       if (ok) {
@@ -1068,15 +1105,27 @@ int pair_heads = 1;
 template <int HALVES>
 int launch(const CUtensorMap& map_q, const CUtensorMap& map_kv, void* out, const int* work, int n_work,
            const int* block_table, int table_stride, int nq, int nkv, int page_size, int num_pages, int window,
-           float scale, int* err, cudaStream_t stream) {
+           float scale, const float* slopes, const float* log_rates, const float* sinks, int* err,
+           cudaStream_t stream) {
   constexpr int KV_BYTES = HALVES * HALF_BYTES;
   const size_t smem = (size_t)KV_BYTES * (1 + 2 * STAGES) + 256 + 3 * 128 * GROUPS * 4 + 1024;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(attention_prefill_tc_kernel<HALVES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(attention_prefill_tc_kernel<HALVES, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem) != cudaSuccess ||
+        cudaFuncSetAttribute(attention_prefill_tc_kernel<HALVES, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem) != cudaSuccess)
       return LS_E_SMEM;
     configured = true;
+  }
+  if (log_rates != nullptr || sinks != nullptr) {
+    // a bias on the scores or a sink: the kernel with a head a block knows them
+    const long long items = (long long)n_work * nq;
+    const int blocks = items < sm_count() ? (int)items : sm_count();
+    LS_COUNT(LS_K_ATTENTION_PREFILL_TC), ls_launch(attention_prefill_tc_kernel<HALVES, true>, dim3(blocks), THREADS, smem, stream, map_q, map_kv,
+              (__nv_bfloat16*)out, work, n_work, block_table, table_stride, nq, nkv, page_size, num_pages, window,
+              scale * 1.4426950408889634f, slopes, log_rates, sinks, err);
+    return ls_launch_status();
   }
   // two heads of a key head in a block where the group size is even and there are items enough
   // to fill the device one and a half times over (with fewer, the longest item would set the
@@ -1101,8 +1150,9 @@ int launch(const CUtensorMap& map_q, const CUtensorMap& map_kv, void* out, const
   // a block per SM (its shared memory and its 512 columns of tensor memory fill one), or fewer items
   const long long items = (long long)n_work * nq;
   const int blocks = items < sm_count() ? (int)items : sm_count();
-  LS_COUNT(LS_K_ATTENTION_PREFILL_TC), ls_launch(attention_prefill_tc_kernel<HALVES>, dim3(blocks), THREADS, smem, stream, map_q, map_kv, (__nv_bfloat16*)out, work, n_work,
-            block_table, table_stride, nq, nkv, page_size, num_pages, window, scale * 1.4426950408889634f, err);
+  LS_COUNT(LS_K_ATTENTION_PREFILL_TC), ls_launch(attention_prefill_tc_kernel<HALVES, false>, dim3(blocks), THREADS, smem, stream, map_q, map_kv, (__nv_bfloat16*)out, work, n_work,
+            block_table, table_stride, nq, nkv, page_size, num_pages, window, scale * 1.4426950408889634f,
+            (const float*)nullptr, (const float*)nullptr, (const float*)nullptr, err);
   return ls_launch_status();
 }
 
@@ -1117,9 +1167,10 @@ LS_API void ls_set_attention_prefill_pairs(int mode) { pair_heads = mode < 0 ? 0
 // launched nothing.
 LS_API int ls_attention_prefill_tc(const void* q, const void* pages, void* out, int tokens, const int* work,
                                    int n_work, const int* block_table, int table_stride, int nq, int nkv, int d,
-                                   int page_size, int num_pages, int window, float scale, int* err,
-                                   cudaStream_t stream) {
+                                   int page_size, int num_pages, int window, float scale, const float* slopes,
+                                   const float* log_rates, const float* sinks, int* err, cudaStream_t stream) {
   if (n_work <= 0 || tokens <= 0) return 0;
+  if ((slopes != nullptr) != (log_rates != nullptr)) return LS_E_SIZE;      // a linear bias alone: the CUDA-core kernels
   if (nq <= 0 || nkv <= 0 || nq % nkv || n_work > 65535) return LS_E_SIZE;
   if (d != 64 && d != 128) return LS_E_SIZE;
   if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64 && page_size != 128) return LS_E_SIZE;
@@ -1131,9 +1182,9 @@ LS_API int ls_attention_prefill_tc(const void* q, const void* pages, void* out, 
   if (!encode(&map_kv, pages, (uint64_t)d, (uint64_t)rows, page_size < BLOCK_N ? page_size : BLOCK_N)) return LS_E_SIZE;
   if (d == 64)
     return launch<1>(map_q, map_kv, out, work, n_work, block_table, table_stride, nq, nkv, page_size, num_pages,
-                     window, scale, err, stream);
+                     window, scale, slopes, log_rates, sinks, err, stream);
   return launch<2>(map_q, map_kv, out, work, n_work, block_table, table_stride, nq, nkv, page_size, num_pages,
-                   window, scale, err, stream);
+                   window, scale, slopes, log_rates, sinks, err, stream);
 }
 
 LS_API const char* ls_constants_attention_prefill_tc() {

@@ -77,10 +77,10 @@ _SIGNATURES["tc"] = {
     "ls_gemm_tc_token_tile": [c_int, c_int, c_int, c_int],
     "ls_gemm_tc_k_shares": [c_int, c_int],
     "ls_attention_decode_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
-                                c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
+                                c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p],
     "ls_attention_prefill_tc_tile_tokens": [],
     "ls_attention_prefill_tc": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
-                                c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
+                                c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "ls_gemm_nt_tc_qkv_heads": [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int, c_float, c_void_p,
                                 c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                 c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -434,17 +434,21 @@ def attention_decode(q, pages, part_acc, part_ml, work, n_work, block_table, nq,
 
 
 def attention_decode_mma(q, pages, part_acc, part_ml, work, n_work, block_table, nq, nkv, d, window,
-                         scale, err) -> bool:
+                         scale, err, slopes=None, log_rates=None) -> bool:
     """Decode attention on mma.sync with TMA-fed pages (csrc/attention_decode_mma.cu): bfloat16,
-    head size 64 or 128, groups up to 16.  Returns False (nothing launched) otherwise."""
+    head size 64 or 128, groups up to 16; ``slopes`` and ``log_rates`` together: the bias that grows
+    with the logarithm of the distance (see ``attention_tile``).  Returns False (nothing launched)
+    otherwise."""
+    if (slopes is None) != (log_rates is None):
+        return False
     if q.dtype != torch.bfloat16 or not USE_TENSOR_CORES[0]:
         return False
     status = library("tc").ls_attention_decode_mma(
         _dev(q, "q"), _dev(pages, "pages", q.dtype), _dev(part_acc, "part_acc", torch.float32),
         _dev(part_ml, "part_ml", torch.float32), _dev(work, "work", torch.int32), n_work,
         _dev(block_table, "block_table", torch.int32), block_table.shape[-1], nq, nkv, d,
-        pages.shape[3], pages.shape[0], int(window), float(scale), _dev(err, "err", torch.int32),
-        _stream())
+        pages.shape[3], pages.shape[0], int(window), float(scale), _slopes(slopes, nq), _slopes(log_rates, nq),
+        _dev(err, "err", torch.int32), _stream())
     if status == -2:
         return False
     _check(status, "attention_decode_mma")
@@ -455,17 +459,21 @@ def attention_prefill_tc_tile_tokens() -> int:
     return int(library("tc").ls_attention_prefill_tc_tile_tokens())
 
 
-def attention_prefill_tc(q, pages, out, work, n_work, block_table, nq, nkv, d, window, scale, err) -> bool:
+def attention_prefill_tc(q, pages, out, work, n_work, block_table, nq, nkv, d, window, scale, err,
+                         slopes=None, log_rates=None, sinks=None) -> bool:
     """Attention of prompt portions on tcgen05 (csrc/attention_prefill_tc.cu): bfloat16, head
-    size 64 or 128, work items of up to 128 tokens.  Returns False (nothing launched) for
-    anything else."""
+    size 64 or 128, work items of up to 128 tokens; ``slopes`` with ``log_rates`` (the bias that
+    grows with the logarithm of the distance) and ``sinks`` as in ``attention_tile``.  Returns
+    False (nothing launched) for anything else."""
+    if (slopes is None) != (log_rates is None):
+        return False
     if q.dtype != torch.bfloat16 or not USE_TENSOR_CORES[0]:
         return False
     status = library("tc").ls_attention_prefill_tc(
         _dev(q, "q"), _dev(pages, "pages", q.dtype), _dev(out, "out", q.dtype), q.shape[0],
         _dev(work, "work", torch.int32), n_work, _dev(block_table, "block_table", torch.int32),
         block_table.shape[-1], nq, nkv, d, pages.shape[3], pages.shape[0], int(window), float(scale),
-        _dev(err, "err", torch.int32), _stream())
+        _slopes(slopes, nq), _slopes(log_rates, nq), _slopes(sinks, nq), _dev(err, "err", torch.int32), _stream())
     if status in (-2, -3):
         return False
     _check(status, "attention_prefill_tc")

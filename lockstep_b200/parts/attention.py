@@ -48,15 +48,16 @@ def _f32(t: torch.Tensor) -> torch.Tensor:
 
 
 class ScoreExtras:
-    """What the CUDA-core attention kernels add to plain scaled scores: a bias that grows with
-    the distance of key and query (``slopes`` alone: linear; with ``log_rates``: logarithmic) and
-    sinks.  Any of them keeps the attention off the tensor-core kernels, which know none."""
+    """What the attention kernels add to plain scaled scores: a bias that grows with the distance
+    of key and query (``slopes`` alone: linear; with ``log_rates``: logarithmic) and sinks.  The
+    tensor-core kernels know the logarithmic bias and sinks; a linear bias keeps the attention on
+    the CUDA-core kernels."""
 
     def __init__(self, slopes=None, log_rates=None, sinks=None):
         self.slopes, self.log_rates, self.sinks = slopes, log_rates, sinks
 
-    def any(self) -> bool:
-        return self.slopes is not None or self.sinks is not None
+    def tensor_cores(self) -> bool:
+        return self.slopes is None or self.log_rates is not None
 
 
 def attend(rt: Runtime, q, ctx, cache, nq: int, nkv: int, d: int, window: int, scale: float, exact: bool,
@@ -66,14 +67,14 @@ def attend(rt: Runtime, q, ctx, cache, nq: int, nkv: int, d: int, window: int, s
     in the engine's type.  ``exact``: every row takes the tile kernel, so that a row's bits do not
     depend on whether it was decoded or part of a prompt."""
     t = q.shape[0]
-    tensor_core_attention = not exact and not extras.any()
+    tensor_core_attention = not exact and extras.tensor_cores()
     attn = rt.rows(t, nq * d)
     plan, done = None, False
     if tensor_core_attention and d in (64, 128):
         plan = ctx.attention_plan(window, K.attention_prefill_tc_tile_tokens())
         done = not plan.n_tile or K.attention_prefill_tc(
             q, cache.pages, attn, plan.tile_work, plan.n_tile, cache.block_table, nq, nkv, d,
-            window, scale, rt.err)
+            window, scale, rt.err, extras.slopes, extras.log_rates, extras.sinks)
     if not done:
         plan = ctx.attention_plan(window)
         if plan.n_tile:
@@ -87,7 +88,7 @@ def attend(rt: Runtime, q, ctx, cache, nq: int, nkv: int, d: int, window: int, s
         if tensor_core_attention:
             done = K.attention_decode_mma(q, cache.pages, part_acc, part_ml, plan.split_work,
                                           plan.n_split, cache.block_table, nq, nkv, d, window,
-                                          scale, rt.err)
+                                          scale, rt.err, extras.slopes, extras.log_rates)
         if not done and not exact:
             done = K.attention_decode(q, cache.pages, part_acc, part_ml, plan.split_work,
                                       plan.n_split, cache.block_table, nq, nkv, d, window,

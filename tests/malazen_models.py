@@ -65,11 +65,12 @@ MODEL_S = model(72, 193, 1e-5, 3, [
 PAGE_S = 16
 
 # T: no loop; a latent layer that sees every key; one norm group; sizes that are no multiples of
-# 8 on the linear side; many query heads on the latent side
+# 8 on the linear side; many query heads on the latent side; a latent and a rotated part that
+# together make a head of 128, which the tensor-core attention takes (bfloat16)
 MODEL_T = model(64, 211, 3e-6, 1, [
     with_mlp(parallel(6, 3, 16, 16, 1, 40, 24, tau=16.0, temp=(0.2, 64), left_scale=0.4, right_scale=0.9), 96, limit=3.0),
     with_mlp(latent(8, 8, 4, 8, 12, scaling=(2.0, 32, 4.0, 0.5)), 48),
-    with_mlp(latent(2, 32, 32, 40, 64, window=33, base=1000.0), 72, limit=1.0),
+    with_mlp(latent(2, 32, 32, 40, 96, window=33, base=1000.0), 72, limit=1.0),
 ])
 PAGE_T = 8
 

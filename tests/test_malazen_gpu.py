@@ -379,12 +379,21 @@ def _softmax_weights(folder, tokens, at=0):
     return plain.biased_attention_mixer(x, w, f"l{at}.mix.left", layer["mixer"]["left"], weights=True)
 
 
+def _tensor_core_attention_launches():
+    from lockstep_b200 import kernels as K
+
+    counts = K.kernel_counts()
+    return counts.get("attention_prefill_tc", 0), counts.get("attention_decode_mma", 0)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("window", [1, 37, 64, 256, None])
-def test_sharp_latent_attention_shows_window_edges_far_keys_and_sinks(zoo, window, dtype):
-    config = M.model(48, 97, 1e-5, 2, [M.with_mlp(M.latent(4, 16, 8, 16, 24, window=window, scale=0.5), 32),
+@pytest.mark.parametrize("window, rank", [(1, 24), (37, 24), (37, 56), (64, 24), (256, 24), (None, 24), (None, 56)])
+def test_sharp_latent_attention_shows_window_edges_far_keys_and_sinks(zoo, window, rank, dtype):
+    # (a latent of 56 and a rotated part of 8 make a head of 64: in bfloat16 the tensor-core kernels)
+    config = M.model(48, 97, 1e-5, 2, [M.with_mlp(M.latent(4, 16, 8, 16, rank, window=window, scale=0.5), 32),
                                        M.with_mlp(M.latent(2, 8, 8, 24, 40, window=(window + 5) if window else 40, scale=0.5))])
-    folder, requests, want = zoo(config, dtype, [620, 300], edit=_sharpen, key=f"sharp-latent{window}")
+    folder, requests, want = zoo(config, dtype, [620, 300], edit=_sharpen, key=f"sharp-latent{window}-{rank}")
+    before = _tensor_core_attention_launches()
     p = _softmax_weights(folder, requests["r0"])                      # [heads, n, n]
     n = p.shape[-1]
     rows = torch.arange(n)[None, :]
@@ -401,6 +410,11 @@ def test_sharp_latent_attention_shows_window_edges_far_keys_and_sinks(zoo, windo
         runner = make_runner(folder, dtype, 16, steps)
         M.assert_close(H.run_plan(runner, steps), want, dtype, f"sharp latent attention, window {window}, {plan_name}",
                        slack=3.0)      # (scores are large: their rounding shows)
+    after = _tensor_core_attention_launches()
+    if rank == 56 and dtype == "bfloat16":
+        assert after[0] > before[0] and after[1] > before[1]       # both tensor-core attention kernels ran
+    else:
+        assert after == before
 
 
 def _sharpen_more_bias(tensors):
@@ -411,11 +425,14 @@ def _sharpen_more_bias(tensors):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_sharp_biased_attention_reaches_far_keys(zoo, dtype):
-    # (behind a layer that rotates: the stream then tells a token's repeats apart)
+@pytest.mark.parametrize("dim", [32, 64])
+def test_sharp_biased_attention_reaches_far_keys(zoo, dim, dtype):
+    # (behind a layer that rotates: the stream then tells a token's repeats apart; heads of 64: in
+    # bfloat16 the tensor-core kernels)
     config = M.model(48, 97, 1e-5, 1, [M.with_mlp(M.latent(2, 16, 8, 16, 24, window=50), 32),
-                                       M.with_mlp(M.parallel(4, 2, 32, 16, 1, 16, 16, scale=0.5, temp=(0.3, 100)), 32)])
-    folder, requests, want = zoo(config, dtype, [700, 280], edit=_sharpen_more_bias, key="sharp-left")
+                                       M.with_mlp(M.parallel(4, 2, dim, 16, 1, 16, 16, scale=0.5, temp=(0.3, 100)), 32)])
+    folder, requests, want = zoo(config, dtype, [700, 280], edit=_sharpen_more_bias, key=f"sharp-left{dim}")
+    before = _tensor_core_attention_launches()
     p = _softmax_weights(folder, requests["r0"], at=1)
     n = p.shape[-1]
     rows = torch.arange(n)[None, :]
@@ -430,6 +447,8 @@ def test_sharp_biased_attention_reaches_far_keys(zoo, dtype):
         steps = PLANS[plan_name](requests)
         runner = make_runner(folder, dtype, 16, steps)
         M.assert_close(H.run_plan(runner, steps), want, dtype, f"sharp biased attention, {plan_name}", slack=3.0)
+    after = _tensor_core_attention_launches()
+    assert (after[0] > before[0] and after[1] > before[1]) == (dim == 64 and dtype == "bfloat16")
 
 
 def _remember(tensors):
