@@ -695,7 +695,7 @@ MALAZEN_SIZES = {
     "w1024": {"width": 1024, "heads": 8, "kv_heads": 4, "linear_heads": 4, "latent_heads": 8, "ff": 3072},
     "w2048": {"width": 2048, "heads": 16, "kv_heads": 4, "linear_heads": 8, "latent_heads": 16, "ff": 6144},
 }
-MALAZEN_RANK, MALAZEN_ROT, MALAZEN_PLAIN, MALAZEN_VALUE, MALAZEN_WINDOW = 192, 64, 64, 128, 1024
+MALAZEN_RANK, MALAZEN_ROT, MALAZEN_PLAIN, MALAZEN_VALUE, MALAZEN_WINDOW = 96, 32, 96, 128, 1024
 
 
 def malazen_configs(z):

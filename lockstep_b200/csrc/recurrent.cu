@@ -334,7 +334,11 @@ __global__ void __launch_bounds__(128) rule_kernel(RuleArgs a) {
     return *reinterpret_cast<const float*>(at);
   };
   auto walk = [&](const float* buf, int c0, int cn) {
-    for (int tt = 0; tt < cn; ++tt) {
+    // unrolled over the chunk: a token's read-out (its sums and the exchange between the lanes of a
+    // column) does not feed the state, so the next tokens' updates are issued beside it
+#pragma unroll
+    for (int tt = 0; tt < CHUNK; ++tt) {
+      if (tt >= cn) break;
       const float* tok = buf + tt * stride;
       const float4* A = reinterpret_cast<const float4*>(tok + part * run);
       const float4* B = reinterpret_cast<const float4*>(tok + dkp + part * run);
