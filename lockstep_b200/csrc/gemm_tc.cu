@@ -151,7 +151,9 @@ struct NormArgs {
   int gain_bf16;           // element type of gain: 1 bfloat16, 0 float32
   int src_rows;
   float eps;
+  int parts;               // the row is normed in this many equal consecutive parts (1: whole), at most NORM_MAX_PARTS
 };
+constexpr int NORM_MAX_PARTS = 4;
 
 template <int BN, int EPI, typename TC>
 __global__ void __launch_bounds__(192, 1)
@@ -466,30 +468,38 @@ __device__ __forceinline__ void normed_rows_to_smem(const NormArgs& norm, const 
     }
     xr[i] = norm.h + (int64_t)src * K;
   }
-  float ss[2] = {0.f, 0.f};
-  for (int g0 = lane; g0 < groups; g0 += 32 * U) {
-    float4 v[2][U];
+  // one sum of squares per part of the row (a norm in parts: rmsnorm_kernel takes each part as a row
+  // of its own, lane l the part's float4 groups l, l + 32, ...); one part is the whole row
+  const int part_groups = groups / norm.parts;
+  float rstd[2][NORM_MAX_PARTS];
 #pragma unroll
-    for (int i = 0; i < 2; ++i)
+  for (int p = 0; p < NORM_MAX_PARTS; ++p) {
+    rstd[0][p] = rstd[1][p] = 0.f;
+    if (p >= norm.parts) continue;
+    float ss[2] = {0.f, 0.f};
+    for (int g0 = lane; g0 < part_groups; g0 += 32 * U) {
+      float4 v[2][U];
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int g = g0 + 32 * u;
-        v[i][u] = (tt[i] >= 0 && g < groups) ? *reinterpret_cast<const float4*>(xr[i] + 4 * g)
-                                             : make_float4(0.f, 0.f, 0.f, 0.f);
-      }
+      for (int i = 0; i < 2; ++i)
 #pragma unroll
-    for (int i = 0; i < 2; ++i)
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (g0 + 32 * u < groups) {
-          ss[i] = fmaf(v[i][u].x, v[i][u].x, ss[i]); ss[i] = fmaf(v[i][u].y, v[i][u].y, ss[i]);
-          ss[i] = fmaf(v[i][u].z, v[i][u].z, ss[i]); ss[i] = fmaf(v[i][u].w, v[i][u].w, ss[i]);
+        for (int u = 0; u < U; ++u) {
+          const int g = g0 + 32 * u;
+          v[i][u] = (tt[i] >= 0 && g < part_groups) ? *reinterpret_cast<const float4*>(xr[i] + 4 * (p * part_groups + g))
+                                                    : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-      }
-  }
-  float rstd[2];
 #pragma unroll
-  for (int i = 0; i < 2; ++i) rstd[i] = 1.0f / sqrtf(ls_warp_sum(ss[i]) / (float)K + norm.eps);
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (g0 + 32 * u < part_groups) {
+            ss[i] = fmaf(v[i][u].x, v[i][u].x, ss[i]); ss[i] = fmaf(v[i][u].y, v[i][u].y, ss[i]);
+            ss[i] = fmaf(v[i][u].z, v[i][u].z, ss[i]); ss[i] = fmaf(v[i][u].w, v[i][u].w, ss[i]);
+          }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) rstd[i][p] = 1.0f / sqrtf(ls_warp_sum(ss[i]) / (float)(4 * part_groups) + norm.eps);
+  }
   int j = 0;
   for (int g = (k_lo >> 2) + lane; g < (k_hi >> 2); g += 32, ++j) {
     float4 v[2];
@@ -507,12 +517,17 @@ __device__ __forceinline__ void normed_rows_to_smem(const NormArgs& norm, const 
     }
     const int k = 4 * g - k_lo;                      // column within the share
     const int kb = k >> 6, kk = k & 63;
+    const int part = norm.parts > 1 ? g / part_groups : 0;
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       if (tt[i] < 0) continue;
       const int t = tt[i];
-      __nv_bfloat162 lo = __floats2bfloat162_rn(v[i].x * rstd[i] * gn.x, v[i].y * rstd[i] * gn.y);
-      __nv_bfloat162 hi = __floats2bfloat162_rn(v[i].z * rstd[i] * gn.z, v[i].w * rstd[i] * gn.w);
+      float r = rstd[i][0];
+#pragma unroll
+      for (int p = 1; p < NORM_MAX_PARTS; ++p)
+        if (part == p) r = rstd[i][p];
+      __nv_bfloat162 lo = __floats2bfloat162_rn(v[i].x * r * gn.x, v[i].y * r * gn.y);
+      __nv_bfloat162 hi = __floats2bfloat162_rn(v[i].z * r * gn.z, v[i].w * r * gn.w);
       uint2 packed;
       packed.x = *reinterpret_cast<uint32_t*>(&lo);
       packed.y = *reinterpret_cast<uint32_t*>(&hi);
@@ -1874,9 +1889,11 @@ LS_API int ls_gemm_nt_tc(const void* X, const void* W, void* C, int c_dtype, int
 // the caller then runs ls_rmsnorm and ls_gemm_nt_tc.
 LS_API int ls_gemm_nt_tc_rmsnorm(const float* h, const int* row_index, int src_rows, const void* gain,
                                  int gain_dtype, float eps, const void* W, void* C, int c_dtype, int T,
-                                 int N, int K, int64_t ldw, int64_t ldc, int epilogue, int* err,
+                                 int N, int K, int64_t ldw, int64_t ldc, int epilogue, int parts, int* err,
                                  cudaStream_t stream) {
   if (gain_dtype != LS_F32 && gain_dtype != LS_BF16) return LS_E_DTYPE;
+  // a norm in parts: equal parts of whole float4 groups, few enough for the kernel's registers
+  if (parts < 1 || parts > NORM_MAX_PARTS || K % (4 * parts)) return LS_E_SIZE;
   NormArgs norm;
   norm.h = h;
   norm.row_index = row_index;
@@ -1884,6 +1901,7 @@ LS_API int ls_gemm_nt_tc_rmsnorm(const float* h, const int* row_index, int src_r
   norm.gain_bf16 = gain_dtype == LS_BF16 ? 1 : 0;
   norm.src_rows = src_rows;
   norm.eps = eps;
+  norm.parts = parts;
   if (epilogue == 3) return LS_E_SIZE;
   return run(nullptr, &norm, nullptr, W, C, c_dtype, T, N, K, 0, ldw, ldc, epilogue, err, stream);
 }
@@ -1905,6 +1923,7 @@ LS_API int ls_gemm_nt_tc_qkv_heads(const void* X, int64_t ldx, const float* h, c
   if (d <= 0 || BM % d || nq <= 0 || nkv <= 0) return LS_E_SIZE;
   if (rot_dim < 0 || rot_dim > d || (rot_dim & 1)) return LS_E_SIZE;
   if (head_gain_dtype != LS_F32 && head_gain_dtype != LS_BF16) return LS_E_DTYPE;
+  const int parts = 1;                   // (the norm in front of this product is one over the whole row)
   LsQkvStore heads;
   heads.q_out = q_out;
   heads.pages = pages;
@@ -1937,5 +1956,6 @@ LS_API int ls_gemm_nt_tc_qkv_heads(const void* X, int64_t ldx, const float* h, c
   norm.gain_bf16 = gain_dtype == LS_BF16 ? 1 : 0;
   norm.src_rows = src_rows;
   norm.eps = eps;
+  norm.parts = parts;
   return run(nullptr, &norm, &heads, W, nullptr, LS_BF16, T, N, K, 0, ldw, 0, 3, err, stream);
 }

@@ -231,7 +231,8 @@ class GQAttention(Mixer):
         # the projection goes through memory and a second kernel does that
         fused = False
         if t <= K.FEW_TOKENS and not self.exact and not interleaved:
-            pending = isinstance(x, NormedRows) and x.pending()
+            # (the product that finishes its heads knows the norm over the whole row only)
+            pending = isinstance(x, NormedRows) and x.pending() and x.groups == 1
             fused = K.gemm_nt_tc_qkv_heads(None if pending else (x.materialize() if isinstance(x, NormedRows) else x),
                                            self.w_qkv, *heads,
                                            normed=(x.h, x.gain, x.eps, x.row_index) if pending else None)

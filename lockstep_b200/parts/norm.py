@@ -20,7 +20,7 @@ class NormedRows:
 
     def __init__(self, norm: "RMSNorm", h: torch.Tensor, row_index=None):
         self.norm, self.h, self.row_index = norm, h, row_index
-        self.gain, self.eps = norm.gain, norm.eps
+        self.gain, self.eps, self.groups = norm.gain, norm.eps, norm.groups
         self._out = None
 
     def pending(self) -> bool:
@@ -35,7 +35,7 @@ class NormedRows:
     def linear(self, w: torch.Tensor, out: torch.Tensor, epilogue: int, err: torch.Tensor) -> None:
         """out = epilogue(norm(h) @ w.T): fused where the kernel allows, else norm, then product."""
         if self._out is None and K.gemm_nt_tc_rmsnorm(self.h, self.gain, self.eps, w, out, epilogue, err,
-                                                      self.row_index):
+                                                      self.row_index, self.groups):
             return
         K.gemm_nt(self.materialize(), w, out, epilogue, err=err)
 
@@ -59,12 +59,8 @@ class RMSNorm(Norm):
         if self.offset:
             self.gain = (self.gain.to(torch.float32) + self.offset).contiguous()
 
-    def lazy(self, h, row_index=None):
-        """The rows of ``h`` to be normalised, for a part that sets ``accepts_normed_rows`` (the
-        products that make the norm themselves know the norm over the whole row only: a norm in
-        groups hands over the finished tensor)."""
-        if self.groups > 1:
-            return self.forward(h, row_index)
+    def lazy(self, h, row_index=None) -> NormedRows:
+        """The rows of ``h`` to be normalised, for a part that sets ``accepts_normed_rows``."""
         return NormedRows(self, h, row_index)
 
     def forward(self, h, row_index=None):
