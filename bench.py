@@ -704,8 +704,8 @@ def malazen_configs(z):
     mlp = {"kind": "dense", "ff": z["ff"], "limit": 7.0}
     par = {"left": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
                     "q_temp": {"coef": 0.1, "every": 1024}},
-           "right": {"heads": z["linear_heads"], "dim": 128, "vdim": 128, "tau": 16.0, "decay_rank": 64},
-           "left_scale": 0.8, "right_scale": 0.9}
+           "right": {"heads": z["linear_heads"], "dim": 128, "vdim": 128, "tau": 8.0, "decay_rank": 64},
+           "left_scale": 1.0, "right_scale": 0.5}
     lat = {"heads": z["latent_heads"], "dim": MALAZEN_PLAIN, "rot_dim": MALAZEN_ROT, "vdim": MALAZEN_VALUE,
            "kv_rank": MALAZEN_RANK, "scale": (MALAZEN_PLAIN + MALAZEN_ROT) ** -0.5, "mask": {"size": MALAZEN_WINDOW},
            "rot": {"dims": MALAZEN_ROT, "base": 1000000.0,

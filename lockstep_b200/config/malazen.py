@@ -111,9 +111,11 @@ class MalazenConfig:
                 left, right = m.get("left"), m.get("right")
                 if not isinstance(left, Mapping) or not isinstance(right, Mapping):
                     raise ConfigError(f"{where}: a parallel mixer needs 'left' and 'right'")
-                _positive(where + ".left", left, "heads", "kv_heads", "dim", "vdim")
+                _positive(where + ".left", left, "heads", "dim", "vdim")
+                if "kv_heads" in left:
+                    _positive(where + ".left", left, "kv_heads")
                 _number(where + ".left", left, "scale")
-                if left["heads"] % left["kv_heads"]:
+                if left["heads"] % left.get("kv_heads", left["heads"]):
                     raise ConfigError(f"{where}.left: heads must be a multiple of kv_heads")
                 temp = left.get("q_temp")
                 if temp is not None:
@@ -154,7 +156,7 @@ class MalazenConfig:
         if layer["type"] == "parallel":
             left, right = m["left"], m["right"]
             attention = PartSpec("gqa_attention", {
-                "hidden_size": width, "num_heads": int(left["heads"]), "num_kv_heads": int(left["kv_heads"]),
+                "hidden_size": width, "num_heads": int(left["heads"]), "num_kv_heads": int(left.get("kv_heads", left["heads"])),
                 "head_dim": int(left["dim"]), "value_dim": int(left["vdim"]), "scale": float(left["scale"]),
                 "window": 0, "qk_norm_eps": None, "bias": True, "q_temp": left.get("q_temp"),
                 "score_bias": "log_distance",

@@ -198,8 +198,8 @@ class GatedLinear(Mixer):
     accepts_normed_rows = True
 
     def __init__(self, hidden_size, num_heads, key_dim, value_dim, tau, norm_eps, runtime: Runtime, decay_rank=None):
-        if key_dim > 256:
-            raise ValueError(f"key_dim {key_dim} is not supported (up to 256)")
+        if key_dim > 512:
+            raise ValueError(f"key_dim {key_dim} is not supported (up to 512)")
         if not float(tau) > 0:
             raise ValueError("tau must be positive")
         self.w, self.H, self.dk, self.dv = int(hidden_size), int(num_heads), int(key_dim), int(value_dim)

@@ -79,7 +79,7 @@ PAGE_T = 8
 # sink only); a width that is no multiple of 8 (no row pitch of 16 bytes: the CUDA-core
 # products also in bfloat16); heads of 64 on the softmax side with eight query heads on one key head
 MODEL_U = model(100, 150, 1e-6, 2, [
-    with_mlp(parallel(8, 1, 64, 64, 2, 64, 64, tau=2.0, temp=(0.4, 1), left_scale=0.8, right_scale=0.9, decay_rank=8), 36),
+    with_mlp(parallel(8, 1, 64, 64, 2, 64, 64, tau=2.0, temp=(0.4, 1), left_scale=0.6, right_scale=1.2, decay_rank=8), 36),
     with_mlp(latent(1, 48, 2, 64, 30, window=1), 50),
     with_mlp(latent(4, 16, 16, 16, 48, window=300, scaling=(8.0, 16, 2.0, 1.0))),
 ], loop=(0, 1, 3))
@@ -90,7 +90,16 @@ MODEL_V = model(48, 97, 1e-5, 2, [
     with_mlp(parallel(2, 1, 16, 32, 1, 16, 16), 32),
 ], loop=(0, 2, 1))
 
-MODELS = {"S": (MODEL_S, PAGE_S), "T": (MODEL_T, PAGE_T), "U": (MODEL_U, PAGE_U), "V": (MODEL_V, 8)}
+# W: odd sizes everywhere: projections with an odd number of rows, heads of 10 and 6, a latent of 21, a
+# rank of 1, a feed-forward of 27, a vocabulary and a width that are no multiples of 8
+MODEL_W = model(52, 101, 2e-6, 4, [
+    with_mlp(latent(3, 10, 6, 14, 21, window=9, base=77.0, scaling=(1.5, 40, 6.0, 0.7)), 27, limit=0.9),
+    with_mlp(parallel(3, 3, 10, 6, 3, 6, 10, tau=3.0, temp=(0.7, 3), left_scale=1.4, right_scale=0.3, decay_rank=1), 30),
+    with_mlp(parallel(5, 1, 24, 40, 1, 10, 6, tau=1.0, temp=(0.1, 50), left_scale=0.2, right_scale=1.0, decay_rank=3)),
+    with_mlp(latent(1, 6, 10, 22, 5), 14),
+], loop=(1, 4, 2))
+
+MODELS = {"S": (MODEL_S, PAGE_S), "T": (MODEL_T, PAGE_T), "U": (MODEL_U, PAGE_U), "V": (MODEL_V, 8), "W": (MODEL_W, 32)}
 
 
 def one_layer(layer, width=48, vocab=97, eps=1e-5, groups=2, loop=None):

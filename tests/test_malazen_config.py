@@ -107,7 +107,7 @@ def test_mixers_side_by_side_keep_a_cache_each():
     cache.audit()
 
 
-@pytest.mark.parametrize("dims, base, scaling", [(16, 50000.0, (2.0, 2048, 32.0, 1.0)), (8, 100.0, (4.0, 64, 8.0, 1.0)),
+@pytest.mark.parametrize("dims, base, scaling", [(16, 40000.0, (3.0, 1024, 16.0, 2.0)), (8, 100.0, (4.0, 64, 8.0, 1.0)),
                                                   (32, 10000.0, None), (4, 1000.0, (8.0, 16, 2.0, 1.0))])
 def test_stretched_rotary_tables(dims, base, scaling):
     from lockstep_b200.parts.position import ScaledRotary
