@@ -511,10 +511,11 @@ LS_API int ls_row_bias(float* x, const void* bias, int bias_dtype, int rows, int
 constexpr int MAX_BRANCHES = 4;
 struct LsBranchScales { float s[MAX_BRANCHES]; };
 __global__ void weighted_sum_kernel(float* __restrict__ residual, const float* __restrict__ branches, int64_t count,
-                                    int n, LsBranchScales scales) {
+                                    int n, LsBranchScales scales, const float* __restrict__ bias, int width) {
   ls_dependency_sync();
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (int64_t)gridDim.x * blockDim.x) {
-    float sum = 0.f;
+    // bias (or null) [width]: the branches' output biases, already weighted and summed
+    float sum = bias != nullptr ? bias[i % width] : 0.f;
 #pragma unroll
     for (int b = 0; b < MAX_BRANCHES; ++b)
       if (b < n) sum = fmaf(scales.s[b], branches[(int64_t)b * count + i], sum);
@@ -523,14 +524,14 @@ __global__ void weighted_sum_kernel(float* __restrict__ residual, const float* _
 }
 
 LS_API int ls_weighted_sum(float* residual, const float* branches, long long count, int n, const float* scales,
-                           cudaStream_t stream) {
+                           const float* bias, int width, cudaStream_t stream) {
   if (count <= 0) return 0;
-  if (n <= 0 || n > MAX_BRANCHES) return LS_E_SIZE;
+  if (n <= 0 || n > MAX_BRANCHES || (bias != nullptr && width <= 0)) return LS_E_SIZE;
   LsBranchScales s;
   for (int b = 0; b < MAX_BRANCHES; ++b) s.s[b] = b < n ? scales[b] : 0.f;
   const int blocks = (int)((count + 255) / 256 < 148 * 16 ? (count + 255) / 256 : 148 * 16);
   LS_COUNT(LS_K_WEIGHTED_SUM);
-  ls_launch(weighted_sum_kernel, blocks, 256, 0, stream, residual, branches, (int64_t)count, n, s);
+  ls_launch(weighted_sum_kernel, blocks, 256, 0, stream, residual, branches, (int64_t)count, n, s, bias, width > 0 ? width : 1);
   return ls_launch_status();
 }
 

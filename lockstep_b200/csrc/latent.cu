@@ -34,6 +34,7 @@ struct LatentArgs {
   const int* block_table;
   int table_stride, H, d, dr, rank, D, page_size, num_pages, max_positions, interleaved, write_cache;
   float eps;
+  const void* w_fold;      // null, or [H, rank, d]: this kernel also folds W_uk into the queries (few tokens)
 };
 
 // element i of a rotated vector x[0 .. dr): pairs (2j, 2j+1) when interleaved, else (j, j + dr/2);
@@ -56,6 +57,7 @@ __device__ __forceinline__ float rotated(const T* x, int i, int dr, int interlea
 template <typename T>
 __global__ void __launch_bounds__(THREADS) latent_finish_kernel(LatentArgs a, int* err) {
   __shared__ float scratch[32];
+  extern __shared__ float q_plain[];       // with w_fold: the plain query part [d] of this block's head
   ls_dependency_sync();
   const int t = blockIdx.x;
   const T* row = reinterpret_cast<const T*>(a.proj) + (int64_t)t * a.ld;
@@ -70,11 +72,45 @@ __global__ void __launch_bounds__(THREADS) latent_finish_kernel(LatentArgs a, in
   const int qd = a.d + a.dr, tail = a.D - a.rank;
   // queries: the rotated part of every head behind the columns the fold will fill, then zeros
   T* q_dst = reinterpret_cast<T*>(a.q_out) + (int64_t)t * a.H * a.D;
-  for (int e = threadIdx.x; e < a.H * tail; e += THREADS) {
+  for (int e = threadIdx.x; e < a.H * tail && blockIdx.y == 0; e += THREADS) {
     const int h = e / tail, i = e - h * tail;
     const float v = i < a.dr ? rotated<T>(row + h * qd + a.d, i, a.dr, a.interleaved, cs, sn) : 0.f;
     q_dst[h * a.D + a.rank + i] = ls_from_float<T>(v);
   }
+  if (a.w_fold != nullptr) {
+    // columns 0 .. rank of head blockIdx.y: W_uk,h^T q_plain,h, an element one chain of fused multiply-adds
+    // over ascending k from zero, as heads_product makes it (the same bits), for a step of few tokens; the
+    // weights come 16 bytes at a time where the rows allow it, several loads in flight
+    const int h = blockIdx.y;
+    for (int e = threadIdx.x; e < a.d; e += THREADS) q_plain[e] = ls_to_float<T>(row[h * qd + e]);
+    __syncthreads();
+    const T* w = reinterpret_cast<const T*>(a.w_fold) + (int64_t)h * a.rank * a.d;
+    constexpr int VEC = 16 / (int)sizeof(T);
+    const bool wide = a.d % VEC == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0;
+    for (int r = threadIdx.x; r < a.rank; r += THREADS) {
+      const T* wr = w + (int64_t)r * a.d;
+      float acc = 0.f;
+      if (wide) {
+        for (int k0 = 0; k0 < a.d; k0 += 4 * VEC) {
+          uint4 raw[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            raw[u] = k0 + u * VEC < a.d ? *reinterpret_cast<const uint4*>(wr + k0 + u * VEC) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (k0 + u * VEC >= a.d) break;
+            const T* wv = reinterpret_cast<const T*>(&raw[u]);
+#pragma unroll
+            for (int x = 0; x < VEC; ++x) acc = fmaf(q_plain[k0 + u * VEC + x], ls_to_float<T>(wv[x]), acc);
+          }
+        }
+      } else {
+        for (int k = 0; k < a.d; ++k) acc = fmaf(q_plain[k], ls_to_float<T>(wr[k]), acc);
+      }
+      q_dst[h * a.D + r] = ls_from_float<T>(acc);
+    }
+  }
+  if (blockIdx.y != 0) return;
   if (!a.write_cache) return;
   const int req = a.token_req[t];
   const int page = a.block_table[(int64_t)req * a.table_stride + pos / a.page_size];
@@ -168,7 +204,7 @@ LS_API int ls_latent_finish(const void* proj, int64_t ld, int dtype, void* q_out
                             int gain_dtype, const float* cos_table, const float* sin_table, const int* positions,
                             const int* token_req, const int* block_table, int table_stride, int tokens, int H, int d,
                             int dr, int rank, int D, int page_size, int num_pages, int max_positions, int interleaved,
-                            int write_cache, float eps, int* err, cudaStream_t stream) {
+                            int write_cache, float eps, const void* w_fold, int* err, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (H <= 0 || d <= 0 || dr < 0 || (dr & 1) || rank <= 0 || D < rank + dr) return LS_E_SIZE;
   if (ld < (int64_t)H * (d + dr) + rank + dr) return LS_E_SIZE;
@@ -180,11 +216,14 @@ LS_API int ls_latent_finish(const void* proj, int64_t ld, int dtype, void* q_out
   a.cos_table = cos_table; a.sin_table = sin_table; a.positions = positions; a.token_req = token_req;
   a.block_table = block_table; a.table_stride = table_stride; a.H = H; a.d = d; a.dr = dr; a.rank = rank; a.D = D;
   a.page_size = page_size > 0 ? page_size : 1; a.num_pages = num_pages; a.max_positions = max_positions;
-  a.interleaved = interleaved; a.write_cache = write_cache; a.eps = eps;
+  a.interleaved = interleaved; a.write_cache = write_cache; a.eps = eps; a.w_fold = w_fold;
+  const size_t smem = w_fold != nullptr ? sizeof(float) * (size_t)d : 0;
+  if (smem > 40 * 1024 || (w_fold != nullptr && H > 65535)) return LS_E_SMEM;
+  const dim3 grid(tokens, w_fold != nullptr ? H : 1);
   LS_COUNT(LS_K_LATENT_FINISH);
   cudaError_t e;
-  if (dtype == LS_F32) e = ls_launch(latent_finish_kernel<float>, dim3(tokens), dim3(THREADS), 0, stream, a, err);
-  else if (dtype == LS_BF16) e = ls_launch(latent_finish_kernel<__nv_bfloat16>, dim3(tokens), dim3(THREADS), 0, stream, a, err);
+  if (dtype == LS_F32) e = ls_launch(latent_finish_kernel<float>, grid, dim3(THREADS), smem, stream, a, err);
+  else if (dtype == LS_BF16) e = ls_launch(latent_finish_kernel<__nv_bfloat16>, grid, dim3(THREADS), smem, stream, a, err);
   else return LS_E_DTYPE;
   if (e != cudaSuccess) return (int)e;
   return ls_launch_status();

@@ -50,7 +50,8 @@ _SIGNATURES = {
         "ls_clamped_glu": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_float,
                            c_void_p, c_void_p, c_int, c_void_p],
         "ls_row_bias": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
-        "ls_weighted_sum": [c_void_p, c_void_p, ctypes.c_longlong, c_int, ctypes.POINTER(c_float), c_void_p],
+        "ls_weighted_sum": [c_void_p, c_void_p, ctypes.c_longlong, c_int, ctypes.POINTER(c_float), c_void_p, c_int,
+                            c_void_p],
         "ls_qk_norm_rope_store": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
                                   c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                   c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
@@ -97,7 +98,7 @@ _SIGNATURES["seq"] = {
                       c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_int, c_float, c_int, c_void_p, c_void_p],
     "ls_latent_finish": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                          c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                         c_int, c_float, c_void_p, c_void_p],
+                         c_int, c_float, c_void_p, c_void_p, c_void_p],
     "ls_heads_product": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int,
                          c_void_p],
     "ls_sigmoid_power_decay": [c_void_p, c_void_p, ctypes.c_longlong, c_int, c_float, c_void_p],
@@ -361,14 +362,17 @@ def row_bias(x, bias, add: bool = False) -> None:
                                  rows, width, 1 if add else 0, _stream()), "row_bias")
 
 
-def weighted_sum(residual, branches, scales) -> None:
-    """residual += sum_b scales[b] * branches[b]; ``branches`` float32 [n, *residual.shape]."""
+def weighted_sum(residual, branches, scales, bias=None) -> None:
+    """residual += sum_b scales[b] * branches[b] (+ bias); ``branches`` float32 [n, *residual.shape], ``bias``
+    float32 [residual.shape[-1]] or None."""
     n = branches.shape[0]
     if tuple(branches.shape[1:]) != tuple(residual.shape) or len(scales) != n:
         raise KernelError("weighted_sum: shapes do not agree")
+    if bias is not None and bias.numel() != residual.shape[-1]:
+        raise KernelError("weighted_sum: the bias does not match the rows")
     _check(library().ls_weighted_sum(_dev(residual, "residual", torch.float32), _dev(branches, "branches", torch.float32),
-                                     residual.numel(), n, (c_float * n)(*[float(v) for v in scales]), _stream()),
-           "weighted_sum")
+                                     residual.numel(), n, (c_float * n)(*[float(v) for v in scales]),
+                                     _opt(bias, "bias", torch.float32), residual.shape[-1], _stream()), "weighted_sum")
 
 
 def _rows(t: torch.Tensor, name: str) -> tuple[int, int]:
@@ -683,13 +687,17 @@ def qkv_finish(qkv, q_out, pages, q_gain, k_gain, cos, sin, positions, token_req
 
 
 def latent_finish(proj, q_out, pages, gain, cos, sin, positions, token_req, block_table, heads: int, d: int, dr: int,
-                  rank: int, pad: int, eps: float, interleaved: bool, write_cache: bool, err) -> None:
+                  rank: int, pad: int, eps: float, interleaved: bool, write_cache: bool, err, w_fold=None) -> None:
     """Between the projections and the attention over a cached latent (csrc/latent.cu).  ``proj`` [tokens, >=
     heads (d + dr) + rank + dr]: every head's plain and rotated query part, then the latent and the shared
     rotated key part.  Writes the rotated query parts (and the padding) to columns rank .. pad of every head of
     ``q_out`` [tokens, heads pad], and [norm(latent) ; rotated key part ; 0] / [norm(latent) ; 0] as the token's
-    key and value rows into ``pages`` [num_pages, 2, 1, page_size, pad]."""
+    key and value rows into ``pages`` [num_pages, 2, 1, page_size, pad].  With ``w_fold`` [heads, rank, d] it also
+    writes columns 0 .. rank of every head, plain query part @ w_fold[head].T, with the bits of ``heads_product`` (for
+    steps of few tokens: every token's block reads all of ``w_fold``)."""
     tokens = proj.shape[0]
+    if w_fold is not None and (tuple(w_fold.shape) != (heads, rank, d) or w_fold.dtype != proj.dtype):
+        raise KernelError("latent_finish: the fold's weights do not match")
     if q_out.shape != (tokens, heads * pad) or q_out.dtype != proj.dtype or gain.numel() != rank:
         raise KernelError("latent_finish: shapes do not agree")
     if write_cache and (pages.dtype != proj.dtype or tuple(pages.shape[1:3]) != (2, 1) or pages.shape[4] != pad):
@@ -703,8 +711,8 @@ def latent_finish(proj, q_out, pages, gain, cos, sin, positions, token_req, bloc
         _dev(positions, "positions", torch.int32), _dev(token_req, "token_req", torch.int32),
         _dev(block_table, "block_table", torch.int32), block_table.shape[-1], tokens, heads, d, dr, rank, pad,
         pages.shape[3] if write_cache else 1, pages.shape[0] if write_cache else 0, cos.shape[0] if dr else 0,
-        1 if interleaved else 0, 1 if write_cache else 0, float(eps), _dev(err, "err", torch.int32), _stream()),
-        "latent_finish")
+        1 if interleaved else 0, 1 if write_cache else 0, float(eps), _opt(w_fold, "w_fold"),
+        _dev(err, "err", torch.int32), _stream()), "latent_finish")
 
 
 def heads_product(a, a_head_stride: int, w, out, out_head_stride: int) -> None:

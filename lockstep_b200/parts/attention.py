@@ -104,6 +104,7 @@ def attend(rt: Runtime, q, ctx, cache, nq: int, nkv: int, d: int, window: int, s
 class GQAttention(Mixer):
     graph_safe = True
     accepts_normed_rows = True
+    can_overwrite = True
 
     def __init__(self, hidden_size, num_heads, num_kv_heads, head_dim, scale, window, qk_norm_eps,
                  position: PositionEncoding, runtime: Runtime, value_dim=None, qk_norm_scope="head",
@@ -213,7 +214,10 @@ class GQAttention(Mixer):
                      bool(cache.writes) and not self.borrows, self.rt.err, bias=self.qkv_bias, q_temp=self.q_temp)
         return q
 
-    def forward(self, x, ctx, cache, residual):
+    def output_bias(self):
+        return self.o_bias
+
+    def forward(self, x, ctx, cache, residual, overwrite=False):
         nq, nkv, d = self.nq, self.nkv, self.pad
         t = residual.shape[0]
         rot = self.position.rotary()
@@ -222,7 +226,7 @@ class GQAttention(Mixer):
             if rot_dim and self.position.rotary_interleaved:
                 raise ValueError("rotation of neighbouring pairs is not available with padded heads")
             q = self._project_wide(x, ctx, cache, t, cos, sin, rot_dim)
-            return self._attend(q, ctx, cache, residual, t)
+            return self._attend(q, ctx, cache, residual, t, overwrite)
         q = self.rt.rows(t, nq * d)
         heads = (q, cache.pages, self.q_gain, self.k_gain, cos, sin, ctx.positions, ctx.token_slot,
                  cache.block_table, nq, nkv, d, rot_dim, self.qk_norm_eps or 0.0, cache.writes, self.rt.err)
@@ -243,11 +247,14 @@ class GQAttention(Mixer):
             else:
                 K.gemm_nt(x, self.w_qkv, qkv, err=self.rt.err)
             K.qk_norm_rope_store(qkv, *heads, interleaved=interleaved)
-        self._attend(q, ctx, cache, residual, t)
+        self._attend(q, ctx, cache, residual, t, overwrite)
 
-    def _attend(self, q, ctx, cache, residual, t):
+    def _attend(self, q, ctx, cache, residual, t, overwrite=False):
         attn = attend(self.rt, q, ctx, cache, self.nq, self.nkv, self.pad, self.window, self.scale, self.exact,
                       self.extras)
+        if overwrite:
+            K.gemm_nt(attn, self.w_o, residual, K.EPILOGUE_STORE, err=self.rt.err)
+            return
         K.gemm_nt(attn, self.w_o, residual, K.EPILOGUE_RESIDUAL, err=self.rt.err)
         if self.o_bias is not None:
             K.row_bias(residual, self.o_bias, add=True)

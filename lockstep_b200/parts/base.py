@@ -167,7 +167,16 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # True for a mixer whose ``forward`` takes ``overwrite=True``: ``residual`` then holds nothing yet and the
+    # mixer stores its result there instead of adding it, without its output projection's bias, which the caller
+    # gets from ``output_bias()`` and adds itself (mixers side by side: one kernel weights and adds them all).
+    can_overwrite = False
+
     def cache_need(self) -> CacheNeed | None:
+        return None
+
+    def output_bias(self) -> torch.Tensor | None:
+        """float32 [hidden] bias of the output projection, or None."""
         return None
 
     def forward(self, x: torch.Tensor, ctx, cache, residual: torch.Tensor) -> None:

@@ -93,10 +93,14 @@ class LatentAttention(Mixer):
         rot = self.position.rotary() if self.dr else None
         cos, sin, _ = rot if rot is not None else (None, None, 0)
         q = rt.rows(t, H * self.pad)
+        # few tokens: the finishing kernel folds W_uk into the queries itself (the same bits, a launch fewer)
+        few = t <= K.FEW_TOKENS and H * self.d * 4 <= 40 * 1024
         K.latent_finish(proj, q, cache.pages, self.gain, cos, sin, ctx.positions, ctx.token_slot, cache.block_table,
                         H, self.d, self.dr, self.rank, self.pad, self.eps,
-                        bool(self.dr and self.position.rotary_interleaved), bool(cache.writes), rt.err)
-        K.heads_product(proj, self.d + self.dr, self.w_fold, q, self.pad)
+                        bool(self.dr and self.position.rotary_interleaved), bool(cache.writes), rt.err,
+                        w_fold=self.w_fold if few else None)
+        if not few:
+            K.heads_product(proj, self.d + self.dr, self.w_fold, q, self.pad)
         attn = attend(rt, q, ctx, cache, H, 1, self.pad, self.window, self.scale, self.exact, self.extras)
         y = rt.rows(t, H * self.dv)
         K.heads_product(attn, self.pad, self.w_up_v, y, self.dv)

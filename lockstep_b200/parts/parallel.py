@@ -4,8 +4,10 @@ sum_b scale_b * mixer_b(x) to the residual stream.
 ``branches``: a list of {"name": tensor-name prefix under the mixer's own, "mixer": PartSpec,
 "position": PartSpec or None, "scale": number}.  Each branch keeps a cache of its own (pages or
 a state slot): the part's need is the branches' needs side by side.  A branch adds its result
-into a float32 buffer of its own as it would into the residual stream (so any registered mixer
-can be a branch); one kernel then adds the weighted buffers to the residual stream.
+into a zeroed float32 buffer of its own as it would into the residual stream (so any registered
+mixer can be a branch); one kernel then adds the weighted buffers to the residual stream.  Where
+every branch can store its result instead (``Mixer.can_overwrite``) nothing is zeroed, and the
+branches' output biases, weighted and summed once when the weights arrive, ride on that kernel.
 """
 
 from __future__ import annotations
@@ -46,10 +48,25 @@ class ParallelMixers(Mixer):
     def bind(self, tensors):
         for name, m in zip(self.names, self.mixers):
             m.bind(own_tensors(name, tensors))
+        self.overwrite = all(m.can_overwrite for m in self.mixers)
+        self.bias = None
+        if self.overwrite:
+            for scale, m in zip(self.scales, self.mixers):
+                b = m.output_bias()
+                if b is not None:
+                    term = scale * b.to(torch.float32)
+                    self.bias = term if self.bias is None else self.bias + term
+            if self.bias is not None:
+                self.bias = self.bias.contiguous()
 
     def forward(self, x, ctx, cache, residual):
         n, t = len(self.mixers), residual.shape[0]
         out = self.rt.rows(n * t, self.w, dtype=torch.float32).view(n, t, self.w)
+        if self.overwrite:
+            for i, m in enumerate(self.mixers):
+                m.forward(x, ctx, cache.parts[i], out[i], overwrite=True)
+            K.weighted_sum(residual, out, self.scales, self.bias)
+            return
         K.row_bias(out.view(n * t, self.w), None)
         for i, m in enumerate(self.mixers):
             m.forward(x, ctx, cache.parts[i], out[i])

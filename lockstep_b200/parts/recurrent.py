@@ -196,6 +196,7 @@ class Wkv(Mixer):
 class GatedLinear(Mixer):
     graph_safe = True
     accepts_normed_rows = True
+    can_overwrite = True
 
     def __init__(self, hidden_size, num_heads, key_dim, value_dim, tau, norm_eps, runtime: Runtime, decay_rank=None):
         if key_dim > 512:
@@ -233,7 +234,7 @@ class GatedLinear(Mixer):
         self.w_a2, self.w_o = t["a2"].contiguous(), t["o"]
         self.a_bias, self.gain = _f32(t["a2.b"]), _f32(t["norm"])
 
-    def forward(self, x, ctx, cache, residual):
+    def forward(self, x, ctx, cache, residual, overwrite=False):
         rt, tokens, at = self.rt, residual.shape[0], self.at
         proj = rt.rows(tokens, self.w_in.shape[0])
         if isinstance(x, NormedRows):
@@ -250,7 +251,7 @@ class GatedLinear(Mixer):
                      None, 0, 0, self.H, self.H, self.dk, self.dv, out_scale=self.dk ** -0.5)
         y = rt.rows(tokens, self.Vd)
         K.head_rms_gate(o, self.gain, None, proj[:, at["g"]:at["g"] + self.Vd], y, self.H, self.dv, True, self.eps)
-        K.gemm_nt(y, self.w_o, residual, K.EPILOGUE_RESIDUAL, err=rt.err)
+        K.gemm_nt(y, self.w_o, residual, K.EPILOGUE_STORE if overwrite else K.EPILOGUE_RESIDUAL, err=rt.err)
 
 
 @register_part("mixer", "gated_linear")
