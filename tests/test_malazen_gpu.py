@@ -506,6 +506,42 @@ def test_greedy_generation_through_the_engine(tmp_path, dtype):
     assert engine.cache.live == 0
 
 
+def test_the_command_line_writes_a_random_model_and_runs_a_workload(tmp_path):
+    """``bin/lockstep random-model`` from a configuration, then ``bin/lockstep run``: greedy tokens are the plain
+    model's, and sampled requests (temperature, top-p) come out whole."""
+    import json
+
+    config, page = M.MODELS["V"]
+    (tmp_path / "config.json").write_text(json.dumps(config))
+    folder = tmp_path / "model"
+    lockstep = [sys.executable, str(ROOT / "bin" / "lockstep")]
+    proc = subprocess.run(lockstep + ["random-model", "--config", str(tmp_path / "config.json"), "--out", str(folder),
+                                      "--seed", "5", "--init-std", "0.15", "--gain-std", "0.1"],
+                          capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    prompts = {f"c{i}": H.random_tokens(n, config["vocab"], 95 + i) for i, n in enumerate([4, 23, 50])}
+    workload = tmp_path / "workload.json"
+    requests = [{"uid": u, "prompt": p, "max_new_tokens": 10} for u, p in prompts.items()]
+    requests += [{"uid": "s0", "prompt": prompts["c1"], "max_new_tokens": 12, "temperature": 0.8, "top_p": 0.9, "seed": 3},
+                 {"uid": "s1", "prompt": prompts["c1"], "max_new_tokens": 12, "temperature": 0.8, "top_p": 0.9, "seed": 3}]
+    workload.write_text(json.dumps(requests))
+    proc = subprocess.run(lockstep + ["run", "--model", str(folder), "--dtype", "float32", "--workload", str(workload),
+                                      "--policy", "fixed-chunk:16", "--num-blocks", "40", "--block-size", str(page),
+                                      "--max-running", "3"], capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = {l["uid"]: l for l in (json.loads(x) for x in proc.stdout.splitlines() if x.startswith("{"))}
+    assert set(lines) == set(prompts) | {"s0", "s1"}
+    cfg, w = plain.read_model_folder(folder)
+    for uid, prompt in prompts.items():
+        got = lines[uid]["generated"]
+        assert len(got) == 10
+        rows = plain.forward(cfg, w, list(prompt) + got)
+        for i, tok in enumerate(got):
+            row = rows[len(prompt) + i - 1]
+            assert float(row[tok]) >= float(row.max()) - 2 * M.TOLERANCE["float32"] * (1 + float(row.abs().max()))
+    assert len(lines["s0"]["generated"]) == 12 and all(0 <= t < config["vocab"] for t in lines["s0"]["generated"])
+
+
 def test_trace_runner_replays_a_trace(tmp_path):
     config, page = M.MODELS["T"]
     folder = M.make_folder(tmp_path, config, seed=9, dtype="bfloat16")
