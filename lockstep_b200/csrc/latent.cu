@@ -144,21 +144,47 @@ __global__ void __launch_bounds__(THREADS) latent_finish_kernel(LatentArgs a, in
 
 // ---------------------------------------------------------------------------------------
 // out[t, h * out_hs + n] = sum_k a[t * a_ld + h * a_hs + k] * w[(h * N + n) * K + k]
-// 64 x 64 outputs a block, 16 of k at a time, 4 x 4 outputs a thread.
+// 64 x 64 outputs a block, 32 of k at a time, 4 x 4 outputs a thread.  Where the rows allow it
+// (`vec`: pitches, head strides and K multiples of a 16-byte piece, aligned bases) both operands
+// come 16 bytes a load, consecutive threads taking consecutive rows, so that the transposed
+// stores into shared memory fall into different banks.
 // ---------------------------------------------------------------------------------------
-constexpr int HP_T = 64, HP_N = 64, HP_K = 16;
+constexpr int HP_T = 64, HP_N = 64, HP_K = 32;
+
+// 64 rows x HP_K columns of `src` (row r at src + r * ld, rows past `rows` and columns past K as zeros)
+// into tile[k][r]
+template <typename T>
+__device__ __forceinline__ void hp_load_tile(float (*tile)[HP_T + 4], const T* __restrict__ src, int64_t ld, int rows,
+                                             int k0, int K, int vec, int tid) {
+  constexpr int VEC = 16 / (int)sizeof(T);
+  if (vec) {
+    for (int p = tid; p < 64 * (HP_K / VEC); p += 256) {
+      const int r = p & 63, c = (p >> 6) * VEC;
+      uint4 raw = make_uint4(0u, 0u, 0u, 0u);             // zero bits are 0.0 in either type
+      if (r < rows && k0 + c < K) raw = *reinterpret_cast<const uint4*>(src + (int64_t)r * ld + k0 + c);
+      const T* v = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int x = 0; x < VEC; ++x) tile[c + x][r] = ls_to_float<T>(v[x]);
+    }
+  } else {
+    for (int e = tid; e < 64 * HP_K; e += 256) {
+      const int r = e / HP_K, k = e - r * HP_K;
+      tile[k][r] = (r < rows && k0 + k < K) ? ls_to_float<T>(src[(int64_t)r * ld + k0 + k]) : 0.f;
+    }
+  }
+}
 
 template <typename T>
 __global__ void __launch_bounds__(256) heads_product_kernel(const T* __restrict__ a, int64_t a_ld, int a_hs,
                                                             const T* __restrict__ w, T* __restrict__ out, int64_t out_ld,
-                                                            int out_hs, int tokens, int N, int K) {
-  __shared__ float As[HP_K][HP_T + 4];
-  __shared__ float Ws[HP_K][HP_N + 4];
+                                                            int out_hs, int tokens, int N, int K, int vec) {
+  __shared__ __align__(16) float As[HP_K][HP_T + 4];
+  __shared__ __align__(16) float Ws[HP_K][HP_N + 4];
   ls_dependency_sync();
   const int h = blockIdx.z, t0 = blockIdx.x * HP_T, n0 = blockIdx.y * HP_N;
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;     // outputs: tokens ty * 4 .., columns tx * 4 ..
-  const T* ah = a + (int64_t)h * a_hs;
-  const T* wh = w + (int64_t)h * N * K;
+  const T* ah = a + (int64_t)h * a_hs + (int64_t)t0 * a_ld;
+  const T* wh = w + ((int64_t)h * N + n0) * K;
   float acc[4][4];
 #pragma unroll
   for (int i = 0; i < 4; ++i)
@@ -166,14 +192,8 @@ __global__ void __launch_bounds__(256) heads_product_kernel(const T* __restrict_
     for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
   for (int k0 = 0; k0 < K; k0 += HP_K) {
     __syncthreads();
-    for (int e = tid; e < HP_T * HP_K; e += 256) {
-      const int r = e / HP_K, k = e - r * HP_K;
-      As[k][r] = (t0 + r < tokens && k0 + k < K) ? ls_to_float<T>(ah[(int64_t)(t0 + r) * a_ld + k0 + k]) : 0.f;
-    }
-    for (int e = tid; e < HP_N * HP_K; e += 256) {
-      const int r = e / HP_K, k = e - r * HP_K;
-      Ws[k][r] = (n0 + r < N && k0 + k < K) ? ls_to_float<T>(wh[(int64_t)(n0 + r) * K + k0 + k]) : 0.f;
-    }
+    hp_load_tile<T>(As, ah, a_ld, tokens - t0, k0, K, vec, tid);
+    hp_load_tile<T>(Ws, wh, K, N - n0, k0, K, vec, tid);
     __syncthreads();
 #pragma unroll
     for (int k = 0; k < HP_K; ++k) {
@@ -236,13 +256,17 @@ LS_API int ls_heads_product(const void* a, int64_t a_ld, int a_hs, const void* w
   const dim3 grid((tokens + HP_T - 1) / HP_T, (N + HP_N - 1) / HP_N, heads);
   if (grid.y > 65535) return LS_E_SIZE;
   LS_COUNT(LS_K_HEADS_PRODUCT);
+  if (dtype != LS_F32 && dtype != LS_BF16) return LS_E_DTYPE;
+  const int piece = dtype == LS_F32 ? 4 : 8;            // elements of 16 bytes
+  const int vec = a_ld % piece == 0 && a_hs % piece == 0 && K % piece == 0 && ((uintptr_t)a & 15) == 0 &&
+                  ((uintptr_t)w & 15) == 0;
   cudaError_t e;
   if (dtype == LS_F32)
     e = ls_launch(heads_product_kernel<float>, grid, dim3(256), 0, stream, (const float*)a, a_ld, a_hs, (const float*)w,
-                  (float*)out, out_ld, out_hs, tokens, N, K);
+                  (float*)out, out_ld, out_hs, tokens, N, K, vec);
   else if (dtype == LS_BF16)
     e = ls_launch(heads_product_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (const __nv_bfloat16*)a, a_ld, a_hs,
-                  (const __nv_bfloat16*)w, (__nv_bfloat16*)out, out_ld, out_hs, tokens, N, K);
+                  (const __nv_bfloat16*)w, (__nv_bfloat16*)out, out_ld, out_hs, tokens, N, K, vec);
   else return LS_E_DTYPE;
   if (e != cudaSuccess) return (int)e;
   return ls_launch_status();
