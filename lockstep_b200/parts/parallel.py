@@ -8,6 +8,9 @@ into a zeroed float32 buffer of its own as it would into the residual stream (so
 mixer can be a branch); one kernel then adds the weighted buffers to the residual stream.  Where
 every branch can store its result instead (``Mixer.can_overwrite``) nothing is zeroed, and the
 branches' output biases, weighted and summed once when the weights arrive, ride on that kernel.
+In a step of few tokens, where every kernel is a handful of blocks and the step is a chain of
+launches, the branches after the first run on streams of their own beside it (in a recorded
+step: branches of the graph) and meet again before the weighted sum.
 """
 
 from __future__ import annotations
@@ -25,6 +28,7 @@ class ParallelMixers(Mixer):
             raise ValueError("one to four mixers can run side by side")
         self.w, self.rt = int(hidden_size), runtime
         self.names, self.scales, self.mixers = [], [], []
+        self._side = None          # streams of the branches after the first, made at first use
         for b in branches:
             position = build_part("position", b.get("position") or PartSpec("none"), runtime)
             self.names.append(str(b["name"]))
@@ -63,8 +67,20 @@ class ParallelMixers(Mixer):
         n, t = len(self.mixers), residual.shape[0]
         out = self.rt.rows(n * t, self.w, dtype=torch.float32).view(n, t, self.w)
         if self.overwrite:
-            for i, m in enumerate(self.mixers):
-                m.forward(x, ctx, cache.parts[i], out[i], overwrite=True)
+            if n > 1 and t <= K.FEW_TOKENS and self.rt.options.get("branch_streams", True):
+                main = torch.cuda.current_stream()
+                if self._side is None:
+                    self._side = [torch.cuda.Stream(device=self.rt.device) for _ in self.mixers[1:]]
+                for i, side in enumerate(self._side, start=1):
+                    side.wait_stream(main)             # x and what came before it
+                    with torch.cuda.stream(side):
+                        self.mixers[i].forward(x, ctx, cache.parts[i], out[i], overwrite=True)
+                self.mixers[0].forward(x, ctx, cache.parts[0], out[0], overwrite=True)
+                for side in self._side:
+                    main.wait_stream(side)
+            else:
+                for i, m in enumerate(self.mixers):
+                    m.forward(x, ctx, cache.parts[i], out[i], overwrite=True)
             K.weighted_sum(residual, out, self.scales, self.bias)
             return
         K.row_bias(out.view(n * t, self.w), None)

@@ -354,6 +354,26 @@ def test_whole_models_in_every_cutting(zoo, model, plan_name, dtype):
         assert runner.graphs.replays > 100               # decoded tokens ran as recorded steps
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_branches_on_streams_of_their_own_give_the_bits_of_branches_in_turn(zoo, dtype):
+    """In steps of few tokens the second mixer of a parallel layer runs on a stream of its own (recorded: a branch
+    of the graph).  The logits are those of a runner that takes the mixers one after the other, bit for bit, in
+    decoding (recorded steps), in portions of a few tokens and in mixed batches."""
+    config, page = M.MODELS["S"]
+    folder, requests, want = zoo(config, dtype, LENGTHS["S"])
+    for plan_name in ("then_single", "portions", "mixed"):
+        steps = PLANS[plan_name](requests)
+        rows = {}
+        for streams in (True, False):
+            runner = make_runner(folder, dtype, page, steps)
+            runner.rt.options["branch_streams"] = streams
+            rows[streams] = H.run_plan(runner, steps)
+            if plan_name == "then_single" and runner.graphs is not None:
+                assert runner.graphs.replays > 100
+        for key, row in rows[True].items():
+            assert torch.equal(row, rows[False][key]), (plan_name, key)
+
+
 def _sharpen(tensors):
     # large query weights make every row of a softmax pick one or two keys: a key that is wrongly
     # seen or not seen at a window's edge, a far key that is lost or a sink that is left out then
